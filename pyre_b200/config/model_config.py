@@ -404,3 +404,202 @@ class PivinexConfig(ModelConfig):
         for rep in range(self.loop_times):
             order += [(i, rep > 0 and i == self.loop_start) for i in range(self.loop_start, self.loop_stop)]
         return order + [(i, False) for i in range(self.loop_stop, len(self.layers))]
+
+
+@dataclass(frozen=True)
+class TekaraxLayer:
+    """One layer of a Tekarax model: which mixer (``kind``: "attention", "wkv" or "latent_attention") with its sizes,
+    and its feed-forward: ``mlp_kind`` "dense" (``ff`` wide, biases, squared relu), "moe" (``experts`` gated experts of
+    ``ff``, ``top`` per token, plus a shared one of ``shared_ff`` when that is positive) or "" (none)."""
+
+    kind: str
+    heads: int
+    dim: int                       # query/key entries per head (wkv: key and value entries per head)
+    vdim: int = 0                  # value entries per head (attention, latent_attention)
+    kv_heads: int = 0              # attention: key/value heads
+    scale: float = 0.0             # factor on q . k
+    rot_dims: int = 0              # attention: leading entries of a head that are rotated (0: no rotation at all)
+    rot_base: float = 10000.0
+    rot_scaling: "tuple | None" = None      # (factor, low, high, original) or None
+    kv_rank: int = 0               # latent_attention: size of the cached latent
+    window: int = 0                # latent_attention: a position sees itself and window - 1 before it (0: all)
+    decay_rank: int = 0            # wkv: inner size of the decay's two-layer map (0: read from the tensor's shape)
+    mlp_kind: str = ""
+    ff: int = 0
+    experts: int = 0
+    top: int = 0
+    shared_ff: int = 0
+
+
+@dataclass(frozen=True)
+class TekaraxConfig(ModelConfig):
+    """A Tekarax decoder: layers with a layer norm before AND after each sublayer and a sigmoid gate per feature on the
+    sublayer's result, x += norm_b(sublayer(norm(x)) * sigmoid(W norm(x) + b)); three kinds of mixer in any order; a
+    span of layers ``loop_start .. loop_stop - 1`` that runs ``loop_times`` times in a row with the same weights, each
+    pass with a cache or state of its own and a learned vector per pass added to the stream before it; a final layer
+    norm and a head.  ``config.json`` keys: ``vocab``, ``width``, ``norm.eps``, ``loop: {start, stop, times}``
+    (optional) and ``layers``, a list of ``{"type", "mixer": {...}, "mlp": {"kind": "dense", "ff"} | {"kind": "moe",
+    "expert": {"ff"}, "router": {experts, top}, "shared": {"ff"}} | null}`` with the mixers
+    ``attention {heads, kv_heads, dim, vdim, scale, rot: {dims, base, scaling: {factor, low, high, original}}}``,
+    ``wkv {heads, dim}`` and ``latent_attention {heads, dim, vdim, kv_rank, scale, mask: {size}}``.  A size that the
+    file does not give (the inner size of a wkv layer's decay map) is read from the shape of the layer's tensor
+    (``with_tensor_shapes``)."""
+
+    architecture: ClassVar[str] = "Tekarax"
+    KINDS: ClassVar[tuple] = ("attention", "wkv", "latent_attention")
+
+    vocab: int
+    width: int
+    norm_eps: float
+    layers: tuple
+    loop_start: int = 0
+    loop_stop: int = 0
+    loop_times: int = 1
+
+    def __post_init__(self):
+        _positive("vocab", self.vocab)
+        _positive("width", self.width)
+        if not self.norm_eps > 0:
+            raise ConfigError(f"config.json: norm.eps must be positive, got {self.norm_eps}")
+        if not self.layers:
+            raise ConfigError("config.json: layers is empty")
+        if not (0 <= self.loop_start <= self.loop_stop <= len(self.layers)) or self.loop_times < 1:
+            raise ConfigError(f"config.json: loop {{start: {self.loop_start}, stop: {self.loop_stop}, times: {self.loop_times}}} "
+                              f"must name a span of the {len(self.layers)} layers and run it at least once")
+        for i, L in enumerate(self.layers):
+            where = f"config.json: layers[{i}]"
+            if L.kind not in self.KINDS:
+                raise ConfigError(f"{where}.type {L.kind!r}: known are {', '.join(self.KINDS)}")
+            if L.heads <= 0 or L.dim <= 0:
+                raise ConfigError(f"{where}.mixer: heads and dim must be positive")
+            if L.kind != "wkv" and (L.vdim <= 0 or not L.scale > 0):
+                raise ConfigError(f"{where}.mixer: vdim and scale must be positive")
+            if L.kind == "attention":
+                if L.kv_heads <= 0 or L.heads % L.kv_heads:
+                    raise ConfigError(f"{where}.mixer.kv_heads ({L.kv_heads}) must divide heads ({L.heads})")
+                if L.rot_dims < 0 or L.rot_dims % 2 or L.rot_dims > L.dim:
+                    raise ConfigError(f"{where}.mixer.rot.dims ({L.rot_dims}) must be even and at most dim ({L.dim})")
+                if L.rot_dims and (not L.rot_base > 0 or L.vdim % 2):
+                    raise ConfigError(f"{where}.mixer.rot: base must be positive and vdim even (the values are rotated too)")
+            if L.kind == "latent_attention" and (L.kv_rank <= 0 or L.window < 0):
+                raise ConfigError(f"{where}.mixer: kv_rank must be positive and mask.size not negative")
+            if L.kind == "wkv" and L.decay_rank < 0:
+                raise ConfigError(f"{where}.mixer.decay_rank must not be negative")
+            if L.mlp_kind not in ("", "dense", "moe"):
+                raise ConfigError(f"{where}.mlp.kind {L.mlp_kind!r}: known are 'dense' and 'moe'")
+            if L.mlp_kind and L.ff <= 0:
+                raise ConfigError(f"{where}.mlp: ff must be positive")
+            if L.mlp_kind == "moe" and (L.experts <= 0 or not 0 < L.top <= L.experts or L.shared_ff < 0):
+                raise ConfigError(f"{where}.mlp.router: {L.experts} experts cannot give top {L.top}")
+
+    @classmethod
+    def from_dict(cls, raw: dict[str, Any]) -> "TekaraxConfig":
+        norm = raw.get("norm")
+        if not isinstance(norm, dict):
+            raise ConfigError("config.json: required key 'norm' (with 'eps') is missing")
+        layers_raw = raw.get("layers")
+        if not isinstance(layers_raw, (list, tuple)):
+            raise ConfigError("config.json: required key 'layers' is missing")
+        layers = []
+        for i, entry in enumerate(layers_raw):
+            where = f"layers[{i}]"
+            if not isinstance(entry, dict) or not isinstance(entry.get("mixer"), dict):
+                raise ConfigError(f"config.json: {where} needs 'type' and 'mixer'")
+            m, kind = entry["mixer"], str(entry.get("type"))
+            fields = dict(kind=kind, heads=_require(m, "heads"), dim=_require(m, "dim"))
+            if kind == "attention":
+                rot = m.get("rot") or {}
+                sc = rot.get("scaling")
+                if sc is not None:
+                    if not isinstance(sc, dict):
+                        raise ConfigError(f"config.json: {where}.mixer.rot.scaling must be an object or null")
+                    sc = tuple(_require(sc, k, float) for k in ("factor", "low", "high", "original"))
+                fields.update(vdim=int(m.get("vdim") or fields["dim"]), kv_heads=int(m.get("kv_heads") or fields["heads"]),
+                              scale=_require(m, "scale", float), rot_dims=int(rot.get("dims", 0)),
+                              rot_base=float(rot.get("base", 10000.0)), rot_scaling=sc)
+            elif kind == "latent_attention":
+                mask = m.get("mask") or {}
+                fields.update(vdim=int(m.get("vdim") or fields["dim"]), kv_rank=_require(m, "kv_rank"),
+                              scale=_require(m, "scale", float), window=int(mask.get("size") or 0))
+            elif kind == "wkv":
+                fields["decay_rank"] = int(m.get("decay_rank") or 0)
+            mlp = entry.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict):
+                    raise ConfigError(f"config.json: {where}.mlp must be an object or null")
+                mk = str(mlp.get("kind", "dense"))
+                fields["mlp_kind"] = mk
+                if mk == "moe":
+                    expert, router = mlp.get("expert"), mlp.get("router")
+                    if not isinstance(expert, dict) or not isinstance(router, dict):
+                        raise ConfigError(f"config.json: {where}.mlp needs 'expert' and 'router'")
+                    shared = mlp.get("shared") or {}
+                    fields.update(ff=_require(expert, "ff"), experts=_require(router, "experts"), top=_require(router, "top"),
+                                  shared_ff=int(shared.get("ff") or 0))
+                else:
+                    fields["ff"] = _require(mlp, "ff")
+            layers.append(TekaraxLayer(**fields))
+        loop = raw.get("loop") or {}
+        start = int(loop.get("start", 0))
+        return cls(vocab=_require(raw, "vocab"), width=_require(raw, "width"), norm_eps=_require(norm, "eps", float),
+                   layers=tuple(layers), loop_start=start, loop_stop=int(loop.get("stop", start)),
+                   loop_times=int(loop.get("times", 1)))
+
+    def to_dict(self) -> dict[str, Any]:
+        layers = []
+        for L in self.layers:
+            if L.kind == "attention":
+                mixer = {"heads": L.heads, "kv_heads": L.kv_heads, "dim": L.dim, "vdim": L.vdim, "scale": L.scale}
+                if L.rot_dims:
+                    mixer["rot"] = {"dims": L.rot_dims, "base": L.rot_base}
+                    if L.rot_scaling:
+                        mixer["rot"]["scaling"] = dict(zip(("factor", "low", "high", "original"), L.rot_scaling))
+            elif L.kind == "latent_attention":
+                mixer = {"heads": L.heads, "dim": L.dim, "vdim": L.vdim, "kv_rank": L.kv_rank, "scale": L.scale}
+                if L.window:
+                    mixer["mask"] = {"size": L.window}
+            else:
+                mixer = {"heads": L.heads, "dim": L.dim}
+                if L.decay_rank:
+                    mixer["decay_rank"] = L.decay_rank
+            mlp = None
+            if L.mlp_kind == "dense":
+                mlp = {"kind": "dense", "ff": L.ff}
+            elif L.mlp_kind == "moe":
+                mlp = {"kind": "moe", "expert": {"ff": L.ff}, "router": {"experts": L.experts, "top": L.top}}
+                if L.shared_ff:
+                    mlp["shared"] = {"ff": L.shared_ff}
+            layers.append({"type": L.kind, "mixer": mixer, "mlp": mlp})
+        out = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.norm_eps},
+               "layers": layers}
+        if self.loop_stop > self.loop_start:
+            out["loop"] = {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times}
+        return out
+
+    def has_loop(self) -> bool:
+        return self.loop_stop > self.loop_start
+
+    def layer_order(self) -> list:
+        """(layer index, number of the pass that starts here or None) in the order the layers run."""
+        if not self.has_loop():
+            return [(i, None) for i in range(len(self.layers))]
+        order = [(i, None) for i in range(self.loop_start)]
+        for rep in range(self.loop_times):
+            order += [(i, rep if i == self.loop_start else None) for i in range(self.loop_start, self.loop_stop)]
+        return order + [(i, None) for i in range(self.loop_stop, len(self.layers))]
+
+    def needs_tensor_shapes(self) -> bool:
+        return any(L.kind == "wkv" and not L.decay_rank for L in self.layers)
+
+    def with_tensor_shapes(self, shape_of) -> "TekaraxConfig":
+        """The configuration with the sizes that only the weights give filled in; ``shape_of(name)`` returns the
+        shape of a checkpoint tensor (or None)."""
+        layers = []
+        for i, L in enumerate(self.layers):
+            if L.kind == "wkv" and not L.decay_rank:
+                shape = shape_of(f"l{i}.mix.w1")
+                if shape is None or len(shape) != 2:
+                    raise ConfigError(f"config.json: layers[{i}] gives no decay_rank and the weights hold no l{i}.mix.w1 to read it from")
+                L = dataclasses.replace(L, decay_rank=int(shape[0]))
+            layers.append(L)
+        return dataclasses.replace(self, layers=tuple(layers))

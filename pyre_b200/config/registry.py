@@ -67,7 +67,13 @@ def load_config(model_dir: str | Path) -> ModelConfig:
     path = Path(model_dir) / "config.json"
     if not path.is_file():
         raise FileNotFoundError(f"no config.json in {Path(model_dir)}")
-    return config_from_dict(json.loads(path.read_text()))
+    config = config_from_dict(json.loads(path.read_text()))
+    # a size that config.json leaves to the weights (the configuration says so) is read from the tensors' shapes
+    if getattr(config, "needs_tensor_shapes", lambda: False)():
+        from ..weights.loader import tensor_shapes
+        shapes = tensor_shapes(model_dir)
+        config = config.with_tensor_shapes(shapes.get)
+    return config
 
 
 _builtin_done = False
@@ -78,4 +84,4 @@ def _ensure_builtin() -> None:
     global _builtin_done
     if not _builtin_done:
         _builtin_done = True
-        from ..models import modovik, pivinex, qwen2  # noqa: F401
+        from ..models import modovik, pivinex, qwen2, tekarax  # noqa: F401

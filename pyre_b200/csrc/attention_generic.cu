@@ -29,7 +29,7 @@ __global__ void paged_attention_generic_kernel(
     int bt_stride,
     const int* seq_of_token,  // [n_tokens]
     const int* positions,     // [n_tokens]
-    int n_tokens, int nh, int nkv, int hd, int page_size, int window, float scale, float sink, long long n_pages, int* err_flag) {
+    int n_tokens, int nh, int nkv, int hd, int page_size, int window, float scale, float sink, const float* head_sinks, long long n_pages, int* err_flag) {
     extern __shared__ float q_smem[];  // [warps][hd]
     pdl_trigger();
     pdl_wait();
@@ -133,8 +133,9 @@ __global__ void paged_attention_generic_kernel(
         for (int i = 0; i < 8; ++i) acc[i] = fmaf(acc[i], alpha, part[i]);
         m = m_new;
     }
-    // a sink: one more term exp(sink - m) in the denominator, with no value (sink = -inf: none, the term is 0)
-    const float inv_l = 1.0f / (l + expf(sink - m));
+    // a sink: one more term exp(sink - m) in the denominator, with no value (sink = -inf: none, the term is 0);
+    // head_sinks: a score per query head instead of the one for all
+    const float inv_l = 1.0f / (l + expf((head_sinks ? head_sinks[h] : sink) - m));
     T* orow = out + ((size_t)t * nh + h) * hd;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -146,8 +147,8 @@ __global__ void paged_attention_generic_kernel(
 PYRE_API int pyre_paged_attention_generic(const void* q, const void* cache, void* out, const int* block_table,
                                           int bt_stride, const int* seq_of_token, const int* positions,
                                           int n_tokens, int nh, int nkv, int hd, int page_size, int window,
-                                          float scale, float sink, int dtype, long long n_pages, int* err_flag,
-                                          cudaStream_t stream) {
+                                          float scale, float sink, const float* head_sinks, int dtype, long long n_pages,
+                                          int* err_flag, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd % 8 || hd > 256 || hd <= 0 || nkv <= 0 || nh % nkv || page_size <= 0) return PYRE_ERR_BAD_ARG;
     const int warps = 4;
@@ -157,11 +158,11 @@ PYRE_API int pyre_paged_attention_generic(const void* q, const void* cache, void
     if (dtype == PYRE_F32)
         pyre_launch(paged_attention_generic_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream, 
             (const float*)q, (const float*)cache, (float*)out, block_table, bt_stride, seq_of_token, positions,
-            n_tokens, nh, nkv, hd, page_size, window, scale, sink, n_pages, err_flag);
+            n_tokens, nh, nkv, hd, page_size, window, scale, sink, head_sinks, n_pages, err_flag);
     else if (dtype == PYRE_BF16)
         pyre_launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, block_table, bt_stride,
-            seq_of_token, positions, n_tokens, nh, nkv, hd, page_size, window, scale, sink, n_pages, err_flag);
+            seq_of_token, positions, n_tokens, nh, nkv, hd, page_size, window, scale, sink, head_sinks, n_pages, err_flag);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;

@@ -126,7 +126,13 @@ struct AttnParams {
     float scale;
     float sink_l2;               // score of a sink without a value, in units of log2(e): 2^(sink_l2 - max) joins every row's
                                  // denominator once, where the row is normalised; -inf: no sink (the term is 0)
+    const float* head_sinks;     // [nh] a sink score per query head (plain units) instead of sink_l2, or null
 };
+
+// the sink's score (base 2) of the row th = token * nh + head
+__device__ __forceinline__ float row_sink_l2(const float* head_sinks, float sink_l2, size_t th, int nh) {
+    return head_sinks ? head_sinks[th % (size_t)nh] * 1.44269504088896341f : sink_l2;
+}
 
 // CLUSTER: the n_splits CTAs of a (group, kv head) form one thread-block cluster and merge their
 // partial results through distributed shared memory; no scratch, no second kernel.
@@ -531,7 +537,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
         }
         const size_t th = (size_t)th_row;
         if (p.n_splits == 1) {
-            const float inv = 1.0f / (L + ex2(p.sink_l2 - m_use));
+            const float inv = 1.0f / (L + ex2(row_sink_l2(p.head_sinks, p.sink_l2, (size_t)th_row, p.nh) - m_use));
             *reinterpret_cast<uint2*>(p.out + th * HD + d) = make_uint2(pack_bf16(O[0] * inv, O[1] * inv), pack_bf16(O[2] * inv, O[3] * inv));
         } else if constexpr (CLUSTER) {
             // push this CTA's partial to the CTA that owns the output dims: slot [this rank][row][d - owner * cp]
@@ -580,7 +586,7 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_mma_kernel(const _
                     L += ml.y * f;
                     O += rx_o[(c * 16 + row) * cp + dl] * f;
                 }
-                p.out[(size_t)th_row * HD + d0 + dl] = __float2bfloat16_rn(O / (L + ex2(p.sink_l2 - m_use)));
+                p.out[(size_t)th_row * HD + d0 + dl] = __float2bfloat16_rn(O / (L + ex2(row_sink_l2(p.head_sinks, p.sink_l2, (size_t)th_row, p.nh) - m_use)));
             }
         }
     }
@@ -595,7 +601,7 @@ constexpr int COMBINE_WARPS = 8;
 __global__ void __launch_bounds__(COMBINE_WARPS * 32)
 combine_splits_kernel(const float* part_acc, const float* part_ml,
                       __nv_bfloat16* out, int n_splits, int hd, int nh,
-                      const int* cu_seqlens, int n_seqs, int max_len, float sink_l2) {
+                      const int* cu_seqlens, int n_seqs, int max_len, float sink_l2, const float* head_sinks) {
     pdl_trigger();
     pdl_wait();
     const size_t th = blockIdx.x;
@@ -655,7 +661,7 @@ combine_splits_kernel(const float* part_acc, const float* part_ml,
             Ls += sm_l[w] * f;
             Os.x += o.x * f; Os.y += o.y * f; Os.z += o.z * f; Os.w += o.w * f;
         }
-        const float inv = 1.0f / (Ls + exp2f(sink_l2 - m_use));
+        const float inv = 1.0f / (Ls + exp2f(row_sink_l2(head_sinks, sink_l2, th, nh) - m_use));
         *reinterpret_cast<uint2*>(out + th * hd + 4 * lane) = make_uint2(pack_bf16(Os.x * inv, Os.y * inv), pack_bf16(Os.z * inv, Os.w * inv));
     }
 }
@@ -753,8 +759,8 @@ PYRE_API long long pyre_attention_mma_scratch_floats(int n_tokens, int nh, int h
 PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* out, float* scratch,
                                       const int* block_table, int bt_stride, const int* cu_seqlens,
                                       const int* positions, int n_tokens, int n_seqs, int nh, int nkv, int hd,
-                                      int page_size, int window, float scale, float sink, int n_splits, int max_len,
-                                      long long n_pages, int uniform_len, int* err_flag, cudaStream_t stream) {
+                                      int page_size, int window, float scale, float sink, const float* head_sinks, int n_splits,
+                                      int max_len, long long n_pages, int uniform_len, int* err_flag, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd % 16 || hd < 16 || hd > 128 || nkv <= 0 || nh % nkv || page_size <= 0 || n_splits < 1) return PYRE_ERR_UNSUPPORTED;
     // without scratch the splits merge through a thread-block cluster (at most 16 CTAs)
@@ -772,6 +778,7 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     p.bt_stride = bt_stride; p.n_seqs = n_seqs; p.nh = nh; p.nkv = nkv; p.page_size = page_size;
     p.window = window; p.n_splits = n_splits; p.scale = scale; p.max_len = max_len;
     p.sink_l2 = sink * 1.44269504088896341f;
+    p.head_sinks = head_sinks;
     p.page_shift = -1;
     if ((page_size & (page_size - 1)) == 0) { p.page_shift = 0; while ((1 << p.page_shift) < page_size) ++p.page_shift; }
     // TMA tiles: power-of-two pages, head size a multiple of 64 (the 128-byte swizzle span), aligned base
@@ -808,7 +815,7 @@ PYRE_API int pyre_paged_attention_mma(const void* q, const void* cache, void* ou
     }
     if (rc) return rc;
     if (n_splits > 1 && !use_cluster) {
-        pyre_launch(combine_splits_kernel, dim3(n_tokens * nh), dim3(COMBINE_WARPS * 32), 0, stream, p.part_acc, p.part_ml, p.out, n_splits, hd, nh, cu_seqlens, n_seqs, max_len, p.sink_l2);
+        pyre_launch(combine_splits_kernel, dim3(n_tokens * nh), dim3(COMBINE_WARPS * 32), 0, stream, p.part_acc, p.part_ml, p.out, n_splits, hd, nh, cu_seqlens, n_seqs, max_len, p.sink_l2, p.head_sinks);
         PYRE_LAUNCH_CHECK();
     }
     return 0;

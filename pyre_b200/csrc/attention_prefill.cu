@@ -59,6 +59,7 @@ struct PrefillParams {
     int bt_stride, n_seqs, nh, nkv, page_size, window, min_len;
     float scale;
     float sink;                  // score of a sink without a value that joins every row's denominator; -inf: none
+    const float* head_sinks;     // [nh] a sink score per query head instead of `sink`, or null
     long long n_pages;           // pages of the pool (0 = not known) and the device's error word: for the debug checks
     int* err_flag;
 };
@@ -274,7 +275,7 @@ __global__ void __launch_bounds__(WARPS * 32, 3) attention_prefill_kernel(const 
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
     // a sink: 2^(sink - max) joins the denominator, with no value (sink = -inf: none)
-    const float sink_l2 = p.sink * 1.44269504088896341f;
+    const float sink_l2 = (p.head_sinks ? p.head_sinks[head] : p.sink) * 1.44269504088896341f;
     const float inv0 = ok0 ? 1.0f / (l_run[0] + exp2f(sink_l2 - m_run[0])) : 0.f, inv1 = ok1 ? 1.0f / (l_run[1] + exp2f(sink_l2 - m_run[1])) : 0.f;
     __nv_bfloat16* out0 = p.out + ((size_t)(tok0 + (ok0 ? r0 : 0)) * p.nh + head) * HD;
     __nv_bfloat16* out1 = p.out + ((size_t)(tok0 + (ok1 ? r1 : 0)) * p.nh + head) * HD;
@@ -306,15 +307,15 @@ int launch(const PrefillParams& p, int tiles_bound, cudaStream_t stream) {
 // head sizes 64 and 128.  n_long_tokens: total tokens of those entries (bounds the grid).
 PYRE_API int pyre_attention_prefill(const void* q, const void* cache, void* out, const int* block_table, int bt_stride,
                                     const int* cu_seqlens, const int* positions, int n_long_tokens, int n_seqs, int nh,
-                                    int nkv, int hd, int page_size, int window, float scale, float sink, int min_len,
-                                    long long n_pages, int* err_flag, cudaStream_t stream) {
+                                    int nkv, int hd, int page_size, int window, float scale, float sink, const float* head_sinks,
+                                    int min_len, long long n_pages, int* err_flag, cudaStream_t stream) {
     if (n_long_tokens <= 0) return 0;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || min_len < 1) return PYRE_ERR_UNSUPPORTED;
     PrefillParams p;
     p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache; p.out = (__nv_bfloat16*)out;
     p.block_table = block_table; p.cu_seqlens = cu_seqlens; p.positions = positions;
     p.bt_stride = bt_stride; p.n_seqs = n_seqs; p.nh = nh; p.nkv = nkv; p.page_size = page_size;
-    p.window = window; p.min_len = min_len; p.scale = scale; p.sink = sink; p.n_pages = n_pages; p.err_flag = err_flag;
+    p.window = window; p.min_len = min_len; p.scale = scale; p.sink = sink; p.head_sinks = head_sinks; p.n_pages = n_pages; p.err_flag = err_flag;
     const int tiles_bound = n_long_tokens / BM + n_seqs;
     return hd == 128 ? launch<128>(p, tiles_bound, stream) : launch<64>(p, tiles_bound, stream);
 }

@@ -180,6 +180,7 @@ struct TcParams {
     float scale;
     float sink_l2;               // score of a sink without a value, in units of log2(e): 2^(sink_l2 - max) joins every row's
                                  // denominator once, where the row is normalised; -inf: none
+    const float* head_sinks;     // [nh] a sink score per query head (plain units) instead of sink_l2, or null
     int* err_flag;
     long long n_pages;           // pages of the pool; read by the debug checks only
     // key_splits > 1: grid.z CTAs share the key tiles of one (query tile, head); each leaves its unnormalised O
@@ -511,7 +512,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
         if (alive) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const float inv = (row_ok && l_sum > 0.f) ? 1.0f / (l_sum + ex2(p.sink_l2 - m_ref)) : 0.f;
+            const float inv = (row_ok && l_sum > 0.f) ? 1.0f / (l_sum + ex2((p.head_sinks ? p.head_sinks[head] * 1.44269504088896341f : p.sink_l2) - m_ref)) : 0.f;
             __nv_bfloat16* orow = p.out + ((size_t)(tok0 + (row_ok ? row : 0)) * p.nh + head) * HD;
             const size_t piece_at = ((size_t)(tok0 + (row_ok ? row : 0)) * p.nh + head) * p.key_splits + blockIdx.z;
             if (p.key_splits > 1 && row_ok) {
@@ -596,7 +597,7 @@ combine_shares_kernel(const TcParams p) {
             }
         }
         if (lane < HD / 4) {
-            const float inv = denom > 0.f ? 1.0f / (denom + ex2(p.sink_l2 - top)) : 0.f;
+            const float inv = denom > 0.f ? 1.0f / (denom + ex2((p.head_sinks ? p.head_sinks[head] * 1.44269504088896341f : p.sink_l2) - top)) : 0.f;
             uint2 packed;
             packed.x = pack_bf16(acc.x * inv, acc.y * inv);
             packed.y = pack_bf16(acc.z * inv, acc.w * inv);
@@ -663,8 +664,8 @@ int launch(const CUtensorMap& mq, const CUtensorMap& mkv, const TcParams& p, int
 PYRE_API int pyre_attention_prefill_tc(const void* q, const void* cache, void* out, const int* block_table,
                                        int bt_stride, const int* cu_seqlens, const int* positions, int n_tokens,
                                        int n_long_tokens, int n_seqs, int nh, int nkv, int hd, int page_size,
-                                       long long n_pages, int window, float scale, float sink, int min_len, int key_splits,
-                                       float* part_o, float* part_ml, int* err_flag, cudaStream_t stream) {
+                                       long long n_pages, int window, float scale, float sink, const float* head_sinks, int min_len,
+                                       int key_splits, float* part_o, float* part_ml, int* err_flag, cudaStream_t stream) {
     if (n_long_tokens <= 0) return 0;
     if ((hd != 64 && hd != 128) || nkv <= 0 || nh % nkv || page_size < 4 || (page_size & (page_size - 1)) || min_len < 1)
         return PYRE_ERR_UNSUPPORTED;
@@ -678,7 +679,7 @@ PYRE_API int pyre_attention_prefill_tc(const void* q, const void* cache, void* o
     p.page_shift = 0;
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.box_rows = page_size < BN ? page_size : BN;
-    p.window = window; p.min_len = min_len; p.scale = scale; p.sink_l2 = sink * 1.44269504088896341f; p.err_flag = err_flag; p.n_pages = n_pages;
+    p.window = window; p.min_len = min_len; p.scale = scale; p.sink_l2 = sink * 1.44269504088896341f; p.head_sinks = head_sinks; p.err_flag = err_flag; p.n_pages = n_pages;
     if (key_splits < 1 || key_splits > 32 || (key_splits > 1 && (!part_o || !part_ml || ((uintptr_t)part_o & 31)))) return PYRE_ERR_BAD_ARG;
     p.key_splits = key_splits; p.part_o = part_o; p.part_ml = part_ml;
     CUtensorMap mq, mkv;

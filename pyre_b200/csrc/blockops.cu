@@ -166,6 +166,10 @@ __device__ __forceinline__ float act_gelu_tanh(float z) {
     return 0.5f * z * (1.0f + tanhf(inner));
 }
 __device__ __forceinline__ float act_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float act_relu2(float z) { return z > 0.f ? z * z : 0.f; }
+__device__ __forceinline__ float act_any(float z, int kind) {
+    return kind == 0 ? act_silu(z) : kind == 1 ? act_gelu_tanh(z) : kind == 2 ? act_relu2(z) : kind == 3 ? tanhf(z) : z;
+}
 
 template <typename T, int KIND>
 __global__ void activation_kernel(const T* in, T* out, size_t n) {
@@ -223,15 +227,17 @@ PYRE_API int pyre_activation(const void* in, void* out, long long n, int kind, i
 //         n = (v * (1 / sqrt(mean(v^2) + eps))) * w; null: no norm
 //   rotation (pairs (j, j + rot / 2), j < rot / 2, after the norm):
 //         out[j] = n[j] cos[j] - n[j + rot/2] sin[j];  out[j + rot/2] = n[j + rot/2] cos[j] + n[j] sin[j]
+//   vcos_t, vsin_t [T, dv / 2] or null: the VALUES are turned too, over all their dv dims (pairs (m, m + dv / 2)),
+//         by tables of their own, and cached so; whoever reads them turns the weighted sum back (head_gate below)
 //   q_out [T, nh, D]; cache: one layer [page][2][nkv][page_size][D]; slot_mapping[t] < 0: store nothing
 // One warp per (token, head); the sum of squares is a warp reduction whose order depends on dk only.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void qk_norm_rope_write_kernel(const T* proj, long long row_stride, int q_col, int k_col, int v_col,
                                           const float* q_w, const float* k_w, float eps, const float* cos_t,
-                                          const float* sin_t, T* q_out, T* cache, const int* slot_mapping, int n_tokens,
-                                          int nh, int nkv, int dk, int dv, int D, int rot, int page_size,
-                                          long long n_pages, int* err_flag) {
+                                          const float* sin_t, const float* vcos_t, const float* vsin_t, T* q_out, T* cache,
+                                          const int* slot_mapping, int n_tokens, int nh, int nkv, int dk, int dv, int D,
+                                          int rot, int page_size, long long n_pages, int* err_flag) {
     extern __shared__ float head_smem[];   // [warps][D]
     pdl_trigger();
     pdl_wait();
@@ -252,8 +258,21 @@ __global__ void qk_norm_rope_write_kernel(const T* proj, long long row_stride, i
         const int kvh = is_k ? h - nh : h - nh - nkv;
         dst = cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + kvh) * page_size + off) * D;
     }
-    if (!is_q && !is_k) {      // a value head: copied, the rest of the row zero
+    if (!is_q && !is_k) {      // a value head: copied (or turned by its own tables), the rest of the row zero
         const T* src = in + v_col + (size_t)(h - nh - nkv) * dv;
+        if (vcos_t) {
+            const int vh = dv / 2;
+            const float* ct = vcos_t + (size_t)t * vh;
+            const float* st = vsin_t + (size_t)t * vh;
+            for (int d = lane; d < D; d += 32) {
+                float o = 0.f;
+                if (d < vh) o = __fadd_rn(__fmul_rn(to_f32<T>(src[d]), ct[d]), __fmul_rn(-to_f32<T>(src[d + vh]), st[d]));
+                else if (d < 2 * vh) o = __fadd_rn(__fmul_rn(to_f32<T>(src[d]), ct[d - vh]), __fmul_rn(to_f32<T>(src[d - vh]), st[d - vh]));
+                else if (d < dv) o = to_f32<T>(src[d]);
+                dst[d] = from_f32<T>(o);
+            }
+            return;
+        }
         for (int d = lane; d < D; d += 32) dst[d] = d < dv ? src[d] : from_f32<T>(0.f);
         return;
     }
@@ -286,22 +305,23 @@ __global__ void qk_norm_rope_write_kernel(const T* proj, long long row_stride, i
 
 PYRE_API int pyre_qk_norm_rope_write(const void* proj, long long row_stride, int q_col, int k_col, int v_col,
                                      const float* q_w, const float* k_w, float eps, const float* cos_t, const float* sin_t,
-                                     void* q_out, void* cache, const int* slot_mapping, int n_tokens, int nh, int nkv,
+                                     const float* vcos_t, const float* vsin_t, void* q_out, void* cache, const int* slot_mapping, int n_tokens, int nh, int nkv,
                                      int dk, int dv, int D, int rot, int page_size, int dtype, long long n_pages,
                                      int* err_flag, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (dk <= 0 || dv <= 0 || D < dk || D < dv || rot < 0 || rot > dk || rot % 2 || page_size <= 0 || nh <= 0 || nkv <= 0)
         return PYRE_ERR_BAD_ARG;
     if (rot && (!cos_t || !sin_t)) return PYRE_ERR_BAD_ARG;
+    if ((vcos_t == nullptr) != (vsin_t == nullptr) || (vcos_t && dv % 2)) return PYRE_ERR_BAD_ARG;
     if (k_col >= 0 && !cache) k_col = -1;
     const int warps = 4;
     const long long items = (long long)n_tokens * (nh + (k_col >= 0 ? 2 * nkv : 0));
     const int blocks = (int)ceil_div_ll(items, warps);
     const size_t smem = (size_t)warps * D * sizeof(float);
     if (dtype == PYRE_BF16)
-        pyre_launch(qk_norm_rope_write_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream, (const __nv_bfloat16*)proj, row_stride, q_col, k_col, v_col, q_w, k_w, eps, cos_t, sin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, n_tokens, nh, nkv, dk, dv, D, rot, page_size, n_pages, err_flag);
+        pyre_launch(qk_norm_rope_write_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream, (const __nv_bfloat16*)proj, row_stride, q_col, k_col, v_col, q_w, k_w, eps, cos_t, sin_t, vcos_t, vsin_t, (__nv_bfloat16*)q_out, (__nv_bfloat16*)cache, slot_mapping, n_tokens, nh, nkv, dk, dv, D, rot, page_size, n_pages, err_flag);
     else if (dtype == PYRE_F32)
-        pyre_launch(qk_norm_rope_write_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream, (const float*)proj, row_stride, q_col, k_col, v_col, q_w, k_w, eps, cos_t, sin_t, (float*)q_out, (float*)cache, slot_mapping, n_tokens, nh, nkv, dk, dv, D, rot, page_size, n_pages, err_flag);
+        pyre_launch(qk_norm_rope_write_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream, (const float*)proj, row_stride, q_col, k_col, v_col, q_w, k_w, eps, cos_t, sin_t, vcos_t, vsin_t, (float*)q_out, (float*)cache, slot_mapping, n_tokens, nh, nkv, dk, dv, D, rot, page_size, n_pages, err_flag);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;
@@ -411,6 +431,157 @@ PYRE_API int pyre_rmsnorm_gate(const float* o, const float* weight, const void* 
         pyre_launch(rmsnorm_gate_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, o, weight, (const __nv_bfloat16*)proj, row_stride, g_col, (__nv_bfloat16*)out, H, eps);
     else if (dtype == PYRE_F32)
         pyre_launch(rmsnorm_gate_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, o, weight, (const float*)proj, row_stride, g_col, (float*)out, H, eps);
+    else return PYRE_ERR_BAD_ARG;
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// out[r, i] = act(in[r, i] + bias[i]) over rows of H entries (bias null: none); kind 0 silu, 1 gelu (tanh form),
+// 2 the square of relu, 3 tanh, 4 none (the bias only).  fp32 arithmetic on the product's result.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void bias_act_kernel(const T* in, const float* bias, T* out, size_t n, int H, int kind) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float z = to_f32<T>(in[i]);
+        if (bias) z += bias[i % (size_t)H];
+        out[i] = from_f32<T>(act_any(z, kind));
+    }
+}
+
+PYRE_API int pyre_bias_act(const void* in, const float* bias, void* out, long long n_rows, int H, int kind, int dtype,
+                           cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0 || kind < 0 || kind > 4) return PYRE_ERR_BAD_ARG;
+    const long long n = n_rows * H;
+    const int blocks = (int)min((long long)148 * 16, ceil_div_ll(n, 256));
+    if (dtype == PYRE_BF16) pyre_launch(bias_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)in, bias, (__nv_bfloat16*)out, (size_t)n, H, kind);
+    else if (dtype == PYRE_F32) pyre_launch(bias_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)in, bias, (float*)out, (size_t)n, H, kind);
+    else return PYRE_ERR_BAD_ARG;
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// x[r, i] += v[i] for every row of the fp32 stream: a vector that a model adds to all tokens at one place of
+// its schedule.
+// ---------------------------------------------------------------------------
+__global__ void add_row_vector_kernel(float* x, const float* v, size_t n, int H) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] += v[i % (size_t)H];
+}
+
+PYRE_API int pyre_add_row_vector(float* x, const float* v, long long n_rows, int H, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0) return PYRE_ERR_BAD_ARG;
+    const long long n = n_rows * H;
+    const int blocks = (int)min((long long)148 * 16, ceil_div_ll(n, 256));
+    pyre_launch(add_row_vector_kernel, dim3(blocks), dim3(256), 0, stream, x, v, (size_t)n, H);
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// A branch's output, gated and normed, as an fp32 update of the stream (not added here: it travels to the next
+// norm's kernel as one fp32 part):
+//   v[i]   = (y[r, i] + y_bias[i]) * sigmoid(g[r, i] + g_bias[i])      y: activation dtype, or the sum of n_partials
+//                                                                      fp32 partial sums; g null: no gate
+//   out[r] = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * w     center = 1 (a layer norm without bias)
+//   out[r] = v / sqrt(mean(v^2) + eps) * w                              center = 0
+// One block per row, the row kept in shared memory; the block size depends on H only, so a row's sums are added in
+// the same order whatever the batch holds.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void gated_norm_kernel(const T* y, const float* partials, int n_partials, long long partial_stride,
+                                  const float* y_bias, const T* g, const float* g_bias, const float* w, float* out, int H,
+                                  float eps, int center) {
+    extern __shared__ float row_smem[];   // [H]
+    __shared__ float scratch[33];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const T* yr = y ? y + (size_t)r * H : nullptr;
+    const float* pr = partials ? partials + (size_t)r * H : nullptr;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = branch_value<T>(yr, pr, n_partials, partial_stride, i);
+        if (y_bias) v += y_bias[i];
+        if (g) v *= act_sigmoid(to_f32<T>(g[(size_t)r * H + i]) + (g_bias ? g_bias[i] : 0.f));
+        row_smem[i] = v;
+        sum += v;
+    }
+    float mean = 0.f;
+    if (center) mean = block_sum(sum, scratch) / (float)H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float d = row_smem[i] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)
+        out[(size_t)r * H + i] = __fmul_rn(__fmul_rn(row_smem[i] - mean, rstd), w[i]);
+}
+
+PYRE_API int pyre_gated_norm(const void* y, const float* partials, int n_partials, long long partial_stride,
+                             const float* y_bias, const void* gate, const float* gate_bias, const float* weight, float* out,
+                             int n_rows, int H, float eps, int center, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if ((y == nullptr) == (partials == nullptr) || (partials && n_partials < 1) || H <= 0 || !weight || !out) return PYRE_ERR_BAD_ARG;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 48 * 1024) return PYRE_ERR_UNSUPPORTED;
+    const int threads = min(512, max(32, ((H / 4 + 31) / 32) * 32));
+    if (dtype == PYRE_BF16)
+        pyre_launch(gated_norm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, (const __nv_bfloat16*)y, partials, n_partials, partial_stride, y_bias, (const __nv_bfloat16*)gate, gate_bias, weight, out, H, eps, center);
+    else if (dtype == PYRE_F32)
+        pyre_launch(gated_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, (const float*)y, partials, n_partials, partial_stride, y_bias, (const float*)gate, gate_bias, weight, out, H, eps, center);
+    else return PYRE_ERR_BAD_ARG;
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// One gate per HEAD on a mixer's output, after turning each head's sum of rotated values back:
+//   u = a[t, h, :dv]                     a head of `a` has a_dim >= dv columns (the rest is dropped)
+//   pairs (m, m + dv / 2) of u turn by MINUS the token's angle (cos, sin [T, dv / 2]; null: no turn)
+//   out[t, h, j] = u[j] * sigmoid(proj[t, g_col + h])          g_col < 0: no gate
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void head_gate_kernel(const T* a, int a_dim, const T* proj, long long row_stride, int g_col, const float* cos_t,
+                                 const float* sin_t, T* out, int n_tokens, int nh, int dv) {
+    pdl_trigger();
+    pdl_wait();
+    const int vh = dv / 2;
+    const size_t n = (size_t)n_tokens * nh * dv, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const size_t t = i / ((size_t)nh * dv);
+        const int c = (int)(i - t * nh * dv), h = c / dv, j = c - h * dv;
+        const T* head = a + (t * nh + h) * a_dim;
+        float u = to_f32<T>(head[j]);
+        if (cos_t) {
+            if (j < vh) u = __fadd_rn(__fmul_rn(u, cos_t[t * vh + j]), __fmul_rn(to_f32<T>(head[j + vh]), sin_t[t * vh + j]));
+            else if (j < 2 * vh) u = __fadd_rn(__fmul_rn(u, cos_t[t * vh + j - vh]), __fmul_rn(-to_f32<T>(head[j - vh]), sin_t[t * vh + j - vh]));
+        }
+        const float gt = g_col >= 0 ? act_sigmoid(to_f32<T>(proj[t * row_stride + g_col + h])) : 1.0f;
+        out[i] = from_f32<T>(u * gt);
+    }
+}
+
+PYRE_API int pyre_head_gate(const void* a, int a_dim, const void* proj, long long row_stride, int g_col, const float* cos_t,
+                            const float* sin_t, void* out, int n_tokens, int nh, int dv, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (a_dim < dv || dv <= 0 || nh <= 0 || (g_col >= 0 && !proj) || (cos_t == nullptr) != (sin_t == nullptr) || (cos_t && dv % 2))
+        return PYRE_ERR_BAD_ARG;
+    const long long n = (long long)n_tokens * nh * dv;
+    const int blocks = (int)min((long long)148 * 16, ceil_div_ll(n, 256));
+    if (dtype == PYRE_BF16)
+        pyre_launch(head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)a, a_dim, (const __nv_bfloat16*)proj, row_stride, g_col, cos_t, sin_t, (__nv_bfloat16*)out, n_tokens, nh, dv);
+    else if (dtype == PYRE_F32)
+        pyre_launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)a, a_dim, (const float*)proj, row_stride, g_col, cos_t, sin_t, (float*)out, n_tokens, nh, dv);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;

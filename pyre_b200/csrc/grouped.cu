@@ -374,12 +374,13 @@ PYRE_API int pyre_grouped_linear(const void* x, long long x_row_stride, long lon
 // The router of a routed feed-forward.  Per token: logits z = W h over all `n_out` router outputs in fp32 (W fp32
 // [n_out, H]; h in the activation dtype), scores s = softmax(z), choice scores s + correction; the `top` outputs
 // with the largest choice scores are chosen (the lowest index wins a tie), and each chosen output's weight is its
-// plain score s times `scale` (not renormalised).  One block per token, one warp per output in turn.
+// plain score s times `scale` (not renormalised).  `sigmoid` != 0: the scores are s = sigmoid(z), each output by itself,
+// instead of the softmax.  One block per token, one warp per output in turn.
 //   idx_out [T, top] int32, weight_out [T, top] fp32
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void route_kernel(const T* h, const float* w, const float* correction, int* idx_out, float* weight_out, int H,
-                             int n_out, int top, float scale) {
+                             int n_out, int top, float scale, int sigmoid) {
     extern __shared__ float z_smem[];   // [n_out] logits, then scores; [n_out] choice scores
     pdl_trigger();
     pdl_wait();
@@ -408,19 +409,24 @@ __global__ void route_kernel(const T* h, const float* w, const float* correction
     }
     __syncthreads();
     if (warp == 0) {
-        float mx = -INFINITY;
-        for (int e = lane; e < n_out; e += 32) mx = fmaxf(mx, z[e]);
-        mx = warp_max(mx);
-        float sum = 0.f;
-        for (int e = lane; e < n_out; e += 32) {
-            const float p = expf(z[e] - mx);
-            z[e] = p;
-            sum += p;
+        float sum = 1.f;
+        if (sigmoid) {
+            for (int e = lane; e < n_out; e += 32) z[e] = 1.0f / (1.0f + expf(-z[e]));
+        } else {
+            float mx = -INFINITY;
+            for (int e = lane; e < n_out; e += 32) mx = fmaxf(mx, z[e]);
+            mx = warp_max(mx);
+            sum = 0.f;
+            for (int e = lane; e < n_out; e += 32) {
+                const float p = expf(z[e] - mx);
+                z[e] = p;
+                sum += p;
+            }
+            sum = warp_sum(sum);
         }
-        sum = warp_sum(sum);
         __syncwarp();
         for (int e = lane; e < n_out; e += 32) {
-            const float s = z[e] / sum;
+            const float s = sigmoid ? z[e] : z[e] / sum;
             z[e] = s;
             choice[e] = s + (correction ? correction[e] : 0.f);
         }
@@ -449,7 +455,7 @@ __global__ void route_kernel(const T* h, const float* w, const float* correction
 }
 
 PYRE_API int pyre_route(const void* h, const float* w, const float* correction, int* idx_out, float* weight_out, int n_tokens,
-                        int H, int n_out, int top, float scale, int dtype, cudaStream_t stream) {
+                        int H, int n_out, int top, float scale, int sigmoid, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (H <= 0 || n_out <= 0 || top <= 0 || top > n_out) return PYRE_ERR_BAD_ARG;
     const size_t smem = (size_t)2 * n_out * sizeof(float);
@@ -457,10 +463,10 @@ PYRE_API int pyre_route(const void* h, const float* w, const float* correction, 
     const int threads = n_tokens >= 512 ? 256 : 1024;      // few tokens: more warps per token's outputs
     if (dtype == PYRE_BF16)
         pyre_launch(route_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), smem, stream, (const __nv_bfloat16*)h, w, correction,
-                    idx_out, weight_out, H, n_out, top, scale);
+                    idx_out, weight_out, H, n_out, top, scale, sigmoid);
     else if (dtype == PYRE_F32)
         pyre_launch(route_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream, (const float*)h, w, correction, idx_out,
-                    weight_out, H, n_out, top, scale);
+                    weight_out, H, n_out, top, scale, sigmoid);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;
@@ -552,6 +558,38 @@ PYRE_API int pyre_combine_pairs(const float* y, const void* h, const int* place_
     else if (dtype == PYRE_F32)
         pyre_launch(combine_pairs_kernel<float>, dim3(blocks), dim3(256), 0, stream, y, (const float*)h, place_of, weight, out,
                     total, H, top);
+    else return PYRE_ERR_BAD_ARG;
+    PYRE_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// The experts' inputs of a routed feed-forward whose weights multiply what an expert READS:
+//   out[place_of[t, k]] = T( weight[t, k] * h[t] )      for every pair with a place (place_of >= 0)
+// out [places, H] in the order of the sorted places, so the products that follow read it without a gather.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void scale_to_places_kernel(const T* h, const int* place_of, const float* weight, T* out, size_t total, int H, int top) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t at = (size_t)blockIdx.x * blockDim.x + threadIdx.x; at < total; at += stride) {
+        const size_t pair = at / H;
+        const int i = (int)(at - pair * H);
+        const int place = place_of[pair];
+        if (place >= 0) out[(size_t)place * H + i] = from_f32<T>(weight[pair] * to_f32<T>(h[(pair / top) * H + i]));
+    }
+}
+
+PYRE_API int pyre_scale_to_places(const void* h, const int* place_of, const float* weight, void* out, int n_tokens, int H, int top,
+                                  int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0 || H <= 0 || top <= 0) return 0;
+    const size_t total = (size_t)n_tokens * top * H;
+    const int blocks = (int)min((long long)pyre_sm_count() * 8, ceil_div_ll((long long)total, 256));
+    if (dtype == PYRE_BF16)
+        pyre_launch(scale_to_places_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)h, place_of, weight, (__nv_bfloat16*)out, total, H, top);
+    else if (dtype == PYRE_F32)
+        pyre_launch(scale_to_places_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)h, place_of, weight, (float*)out, total, H, top);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;

@@ -40,6 +40,7 @@ LIBRARIES = {
     "parallel_block": "parallel_block.cu",
     "latent_attention": "latent_attention.cu",
     "grouped": "grouped.cu",
+    "wkv": "wkv.cu",
 }
 
 HEADERS = ["common.cuh", "attention_mma_noalloc.h"]

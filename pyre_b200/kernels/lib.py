@@ -38,17 +38,23 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_scale_rows": ("elementwise", [P, P, I, P, I, I, F, P]),
     "pyre_sample": ("sampling", [P, LL, P, P, P, P, I, I, P, P]),
     "pyre_sample_slices": ("sampling", [I]),
-    "pyre_paged_attention_generic": ("attention_generic", [P, P, P, P, I, P, P, I, I, I, I, I, I, F, F, I, LL, P, P]),
+    "pyre_paged_attention_generic": ("attention_generic", [P, P, P, P, I, P, P, I, I, I, I, I, I, F, F, P, I, LL, P, P]),
     "pyre_sgemm_nt": ("gemm_f32", [P, LL, P, LL, P, LL, P, I, I, I, P]),
-    "pyre_paged_attention_mma": ("attention_mma", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, F, I, I, LL, I, P, P]),
-    "pyre_attention_prefill_tc": ("attention_tc", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, LL, I, F, F, I, I, P, P, P, P]),
-    "pyre_attention_prefill": ("attention_prefill", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, F, I, LL, P, P]),
+    "pyre_paged_attention_mma": ("attention_mma", [P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, F, P, I, I, LL, I, P, P]),
+    "pyre_attention_prefill_tc": ("attention_tc", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, LL, I, F, F, P, I, I, P, P, P, P]),
+    "pyre_attention_prefill": ("attention_prefill", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, F, P, I, LL, P, P]),
     "pyre_cast_rows": ("blockops", [P, P, LL, I, P]),
     "pyre_norm_add": ("blockops", [P, P, P, I, LL, P, P, I, I, F, I, P]),
     "pyre_activation": ("blockops", [P, P, LL, I, I, P]),
-    "pyre_qk_norm_rope_write": ("blockops", [P, LL, I, I, I, P, P, F, P, P, P, P, P, I, I, I, I, I, I, I, I, I, LL, P, P]),
+    "pyre_qk_norm_rope_write": ("blockops", [P, LL, I, I, I, P, P, F, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, LL, P, P]),
     "pyre_sigmoid_gate": ("blockops", [P, I, P, LL, I, P, I, I, I, I, P]),
     "pyre_rmsnorm_gate": ("blockops", [P, P, P, LL, I, P, I, I, F, I, P]),
+    "pyre_head_gate": ("blockops", [P, I, P, LL, I, P, P, P, I, I, I, I, P]),
+    "pyre_bias_act": ("blockops", [P, P, P, LL, I, I, I, P]),
+    "pyre_add_row_vector": ("blockops", [P, P, LL, I, P]),
+    "pyre_gated_norm": ("blockops", [P, P, I, LL, P, P, P, P, P, I, I, F, I, I, P]),
+    "pyre_token_shift_mix": ("wkv", [P, P, LL, LL, P, P, P, P, P, I, I, I, I, P]),
+    "pyre_wkv_scan": ("wkv", [P, P, P, P, P, P, P, P, P, LL, LL, P, P, P, P, I, I, I, I, I, F, I, P]),
     "pyre_linear_attention_scan": ("linear_attention", [P, LL, I, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P]),
     "pyre_linear_attention_chunked": ("linear_attention", [P, LL, I, I, I, P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "pyre_add_layernorm": ("parallel_block", [P, P, P, I, P, P, P, I, P, LL, P, P, I, P, I, I, F, I, I, P]),
@@ -59,7 +65,8 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_latent_attention_exact": ("latent_attention", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, LL, P, P]),
     "pyre_latent_attention_mma": ("latent_attention", [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, I, I, LL, P, P]),
     "pyre_grouped_linear": ("grouped", [P, LL, LL, P, LL, P, LL, LL, P, P, P, I, I, I, I, I, I, I, I, P]),
-    "pyre_route": ("grouped", [P, P, P, P, P, I, I, I, I, F, I, P]),
+    "pyre_route": ("grouped", [P, P, P, P, P, I, I, I, I, F, I, I, P]),
+    "pyre_scale_to_places": ("grouped", [P, P, P, P, I, I, I, I, P]),
     "pyre_group_pairs": ("grouped", [P, I, I, I, P, P, P, P]),
     "pyre_combine_pairs": ("grouped", [P, P, P, P, P, I, I, I, I, P]),
 }
@@ -86,7 +93,9 @@ DEFAULT_CLASS = {
     "pyre_linear_attention_chunked": "linear_attention",
     "pyre_add_layernorm": "norm", "pyre_scaled_sum": "norm", "pyre_act_mul": "activation", "pyre_latent_prepare": "rotary+write",
     "pyre_latent_rotate_q": "rotary+write", "pyre_latent_attention_exact": "attention", "pyre_latent_attention_mma": "attention", "pyre_grouped_linear": "grouped_product",
-    "pyre_route": "router", "pyre_group_pairs": "router", "pyre_combine_pairs": "router",
+    "pyre_route": "router", "pyre_group_pairs": "router", "pyre_combine_pairs": "router", "pyre_scale_to_places": "router",
+    "pyre_head_gate": "gate", "pyre_bias_act": "activation", "pyre_add_row_vector": "norm", "pyre_gated_norm": "norm",
+    "pyre_token_shift_mix": "recurrence", "pyre_wkv_scan": "recurrence",
 }
 
 

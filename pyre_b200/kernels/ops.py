@@ -370,7 +370,8 @@ def paged_attention_generic(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
                             head_dim: int, scale: float, window: "int | None" = None,
                             out: "torch.Tensor | None" = None, sink: "float | None" = None) -> torch.Tensor:
     """Exact fp32-arithmetic attention of every query token over its sequence's pages.  ``sink``: the score of a
-    sink that has no value: exp(sink) joins every softmax denominator (None: no sink)."""
+    sink that has no value: exp(sink) joins every softmax denominator (None: no sink; a float32 tensor [n_heads]: a
+    score per query head)."""
     _check(q, "q", dim=2)
     _check(cache_layer, "cache_layer", q.dtype, 5)
     _check(block_table, "block_table", torch.int32, 2)
@@ -390,7 +391,7 @@ def paged_attention_generic(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
         out = torch.empty_like(q)
     lib.call("pyre_paged_attention_generic", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(),
              block_table.data_ptr(), block_table.stride(0), seq_of_token.data_ptr(), positions.data_ptr(), T,
-             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _sink(sink), _dt(q.dtype), cache_layer.shape[0],
+             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _sink_args(sink, n_heads)[0], _sink_args(sink, n_heads)[1], _dt(q.dtype), cache_layer.shape[0],
              device_error_flag(q.device).data_ptr(), _stream())
     return out
 
@@ -398,6 +399,17 @@ def paged_attention_generic(q: torch.Tensor, cache_layer: torch.Tensor, block_ta
 def _sink(sink: "float | None") -> float:
     """The kernels' encoding of 'no sink': a score of minus infinity, whose term in the denominator is zero."""
     return float("-inf") if sink is None else float(sink)
+
+
+def _sink_args(sink, n_heads: int) -> tuple:
+    """(one score for all heads, pointer to a score per query head or None) as the attention kernels take them:
+    ``sink`` is None, a number, or a float32 tensor [n_heads] on the device."""
+    if isinstance(sink, torch.Tensor):
+        _check(sink, "sink", torch.float32, 1)
+        if sink.shape[0] != n_heads:
+            raise ValueError(f"{sink.shape[0]} sink scores for {n_heads} query heads")
+        return float("-inf"), sink.data_ptr()
+    return _sink(sink), None
 
 
 MMA_MAX_HEAD_DIM = 128
@@ -499,7 +511,7 @@ def paged_attention_mma(q: torch.Tensor, cache_layer: torch.Tensor, block_table:
             raise ValueError(f"scratch must be {need} contiguous floats")
     lib.call("pyre_paged_attention_mma", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), _ptr(scratch),
              block_table.data_ptr(), block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), T, n_seqs,
-             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _sink(sink), n_splits, int(max_len),
+             n_heads, n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _sink_args(sink, n_heads)[0], _sink_args(sink, n_heads)[1], n_splits, int(max_len),
              cache_layer.shape[0], int(uniform_len), device_error_flag(q.device).data_ptr(), _stream())
     return out
 
@@ -531,7 +543,7 @@ def attention_prefill(q: torch.Tensor, cache_layer: torch.Tensor, block_table: t
         raise ValueError("out, cu_seqlens and positions do not match the batch")
     lib.call("pyre_attention_prefill", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), block_table.data_ptr(),
              block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), int(n_long_tokens), n_seqs, n_heads,
-             n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _sink(sink), int(min_len), cache_layer.shape[0],
+             n_kv_heads, head_dim, page_size, int(window or 0), float(scale), _sink_args(sink, n_heads)[0], _sink_args(sink, n_heads)[1], int(min_len), cache_layer.shape[0],
              device_error_flag(q.device).data_ptr(), _stream())
     return out
 
@@ -594,7 +606,7 @@ def attention_prefill_tc(q: torch.Tensor, cache_layer: torch.Tensor, block_table
         part_ml = torch.empty((q.shape[0], n_heads, key_splits, 2), dtype=torch.float32, device=q.device)
     lib.call("pyre_attention_prefill_tc", q.data_ptr(), cache_layer.data_ptr(), out.data_ptr(), block_table.data_ptr(),
              block_table.stride(0), cu_seqlens.data_ptr(), positions.data_ptr(), q.shape[0], int(n_long_tokens), n_seqs,
-             n_heads, n_kv_heads, head_dim, page_size, cache_layer.shape[0], int(window or 0), float(scale), _sink(sink), int(min_len),
+             n_heads, n_kv_heads, head_dim, page_size, cache_layer.shape[0], int(window or 0), float(scale), _sink_args(sink, n_heads)[0], _sink_args(sink, n_heads)[1], int(min_len),
              key_splits, _ptr(part_o), _ptr(part_ml), device_error_flag(q.device).data_ptr(), _stream())
     return out
 
@@ -1140,16 +1152,26 @@ def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
 def qk_norm_rope_write(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, q_weight: "torch.Tensor | None",
                        k_weight: "torch.Tensor | None", eps: float, cos: "torch.Tensor | None", sin: "torch.Tensor | None",
                        cache_layer: "torch.Tensor | None", slot_mapping: "torch.Tensor | None", n_heads: int,
-                       n_kv_heads: int, qk_dim: int, v_dim: int, row_dim: int, rotary_dim: int, page_size: int) -> torch.Tensor:
+                       n_kv_heads: int, qk_dim: int, v_dim: int, row_dim: int, rotary_dim: int, page_size: int,
+                       v_cos: "torch.Tensor | None" = None, v_sin: "torch.Tensor | None" = None) -> torch.Tensor:
     """Per-head RMS norm of queries and keys (weights [qk_dim], shared by the heads; None: no norm), rotation of
     the first ``rotary_dim`` dims of each head, and the paged write, for heads whose query/key size ``qk_dim`` and
     value size ``v_dim`` differ from the cache's row size ``row_dim`` (the rest of a row is zero).
     ``proj`` [T, W] holds the token's projections: queries at column ``q_col``, keys at ``k_col``, values at ``v_col``.
     ``cache_layer`` None: nothing is stored and no keys or values are read from ``proj`` (a layer that reads another
-    layer's cache).  Returns the queries [T, n_heads * row_dim]."""
+    layer's cache).  ``v_cos`` / ``v_sin`` [T, v_dim / 2]: the values are turned too, over all their dims in
+    half-split pairs, by these tables, and cached so (``head_gate`` turns a head's weighted sum back).
+    Returns the queries [T, n_heads * row_dim]."""
     _check(proj, "proj", dim=2)
     T, W = proj.shape
     D = int(row_dim)
+    if (v_cos is None) != (v_sin is None):
+        raise ValueError("value tables come in pairs")
+    if v_cos is not None:
+        _check(v_cos, "v_cos", torch.float32, 2)
+        _check(v_sin, "v_sin", torch.float32, 2)
+        if v_dim % 2 or tuple(v_cos.shape) != (T, v_dim // 2) or tuple(v_sin.shape) != (T, v_dim // 2):
+            raise ValueError(f"v_cos/v_sin must be [{T}, {v_dim // 2}] for values of an even size")
     write = cache_layer is not None
     if write:
         _check(cache_layer, "cache_layer", proj.dtype, 5)
@@ -1182,7 +1204,7 @@ def qk_norm_rope_write(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, q
     q_out = torch.empty((T, n_heads * D), dtype=proj.dtype, device=proj.device)
     lib.call("pyre_qk_norm_rope_write", proj.data_ptr(), W, int(q_col), int(k_col) if write else -1, int(v_col) if write else -1,
              _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(cos) if rotary_dim else None, _ptr(sin) if rotary_dim else None,
-             q_out.data_ptr(), _ptr(cache_layer), _ptr(slot_mapping) if write else None, T, n_heads,
+             _ptr(v_cos), _ptr(v_sin), q_out.data_ptr(), _ptr(cache_layer), _ptr(slot_mapping) if write else None, T, n_heads,
              n_kv_heads, qk_dim, v_dim, D, rotary_dim, page_size, _dt(proj.dtype),
              cache_layer.shape[0] if write else 0, device_error_flag(proj.device).data_ptr(), _stream())
     return q_out
@@ -1203,6 +1225,103 @@ def sigmoid_gate(a: torch.Tensor, a_dim: int, proj: "torch.Tensor | None", g_col
     out = torch.empty((T, n_heads * v_dim), dtype=a.dtype, device=a.device)
     lib.call("pyre_sigmoid_gate", a.data_ptr(), int(a_dim), _ptr(proj), proj.shape[1] if proj is not None else 0,
              int(g_col) if proj is not None else -1, out.data_ptr(), T, n_heads, v_dim, _dt(a.dtype), _stream())
+    return out
+
+
+def head_gate(a: torch.Tensor, a_dim: int, proj: "torch.Tensor | None", g_col: int, n_heads: int, v_dim: int,
+              cos: "torch.Tensor | None" = None, sin: "torch.Tensor | None" = None) -> torch.Tensor:
+    """out[t, h, :] = turn_back(a[t, h, :v_dim]) * sigmoid(proj[t, g_col + h]): ONE gate per head (``proj`` None: no
+    gate); with ``cos`` / ``sin`` [T, v_dim / 2] the half-split pairs of a head are turned by minus the token's
+    angles first (the sum of values that were cached rotated).  A head of ``a`` has ``a_dim`` columns, of which the
+    first ``v_dim`` count.  Returns [T, n_heads * v_dim]."""
+    _check(a, "a", dim=2)
+    T = a.shape[0]
+    if a.shape[1] != n_heads * a_dim or a_dim < v_dim:
+        raise ValueError("the heads do not match the tensor")
+    if proj is not None:
+        _check(proj, "proj", a.dtype, 2)
+        if proj.shape[0] != T or g_col < 0 or g_col + n_heads > proj.shape[1]:
+            raise ValueError("the gates do not lie inside the projection row")
+    if (cos is None) != (sin is None):
+        raise ValueError("tables come in pairs")
+    if cos is not None:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if v_dim % 2 or tuple(cos.shape) != (T, v_dim // 2) or tuple(sin.shape) != (T, v_dim // 2):
+            raise ValueError(f"cos/sin must be [{T}, {v_dim // 2}] for values of an even size")
+    out = torch.empty((T, n_heads * v_dim), dtype=a.dtype, device=a.device)
+    lib.call("pyre_head_gate", a.data_ptr(), int(a_dim), _ptr(proj), proj.shape[1] if proj is not None else 0,
+             int(g_col) if proj is not None else -1, _ptr(cos), _ptr(sin), out.data_ptr(), T, n_heads, v_dim, _dt(a.dtype), _stream())
+    return out
+
+
+BIAS_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2, "tanh": 3, None: 4}
+
+
+def bias_act(x: torch.Tensor, bias: "torch.Tensor | None", kind: "str | None") -> torch.Tensor:
+    """act(x + bias) over rows, fp32 arithmetic on a product's result: ``silu``, ``gelu_tanh``, ``relu2`` (the square
+    of relu), ``tanh`` or None (the bias only); ``bias`` fp32 [H] or None."""
+    _check(x, "x", dim=2)
+    if kind not in BIAS_ACTIVATIONS:
+        raise UnsupportedSize(f"activation {kind!r}: implemented are {sorted(k for k in BIAS_ACTIVATIONS if k)}")
+    T, H = x.shape
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != H:
+            raise ValueError(f"bias has {bias.shape[0]} entries, rows have {H}")
+    out = torch.empty_like(x)
+    lib.call("pyre_bias_act", x.data_ptr(), _ptr(bias), out.data_ptr(), T, H, BIAS_ACTIVATIONS[kind], _dt(x.dtype), _stream())
+    return out
+
+
+def add_row_vector(x: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """x[t] += v for every row of the fp32 stream ``x`` [T, H], in place."""
+    _check(x, "x", torch.float32, 2)
+    _check(v, "v", torch.float32, 1)
+    if v.shape[0] != x.shape[1]:
+        raise ValueError(f"a vector of {v.shape[0]} entries for rows of {x.shape[1]}")
+    lib.call("pyre_add_row_vector", x.data_ptr(), v.data_ptr(), x.shape[0], x.shape[1], _stream())
+    return x
+
+
+def gated_norm(y: "torch.Tensor | PartialSums | DeferredProduct", y_bias: "torch.Tensor | None", gate: "torch.Tensor | None",
+               gate_bias: "torch.Tensor | None", weight: torch.Tensor, eps: float, act_dtype: torch.dtype,
+               center: bool = True) -> torch.Tensor:
+    """norm((y + y_bias) * sigmoid(gate + gate_bias)) * weight per row, as fp32 [T, H]: a branch's output (activation
+    dtype, or fp32 partial sums that the kernel adds) gated element by element and normed, ready to be added to the
+    stream.  ``center``: a layer norm without bias (mean taken off, variance of the deviations); else an RMS norm.
+    ``gate`` None: no gate."""
+    _check(weight, "weight", torch.float32, 1)
+    H = weight.shape[0]
+    if isinstance(y, DeferredProduct):
+        y = y.partials()
+    parts, n_parts, stride = None, 0, 0
+    if isinstance(y, PartialSums):
+        parts, n_parts, y = y.parts, y.n, None
+        T = parts.shape[1]
+        stride, device = T * H, parts.device
+        if parts.shape[2] != H:
+            raise ValueError(f"branch output rows of {parts.shape[2]}, norm weight of {H}")
+    else:
+        _check(y, "y", act_dtype, 2)
+        T, device = y.shape[0], y.device
+        if y.shape[1] != H:
+            raise ValueError(f"branch output rows of {y.shape[1]}, norm weight of {H}")
+    for b, name in ((y_bias, "y_bias"), (gate_bias, "gate_bias")):
+        if b is not None:
+            _check(b, name, torch.float32, 1)
+            if b.shape[0] != H:
+                raise ValueError(f"{name} has {b.shape[0]} entries, rows have {H}")
+    if gate is not None:
+        _check(gate, "gate", act_dtype, 2)
+        if tuple(gate.shape) != (T, H):
+            raise ValueError(f"gate {tuple(gate.shape)} != branch output {(T, H)}")
+    if H * 4 > 48 * 1024:
+        raise UnsupportedSize(f"rows of {H}: the gated norm takes up to 12,288 entries")
+    out = torch.empty((T, H), dtype=torch.float32, device=device)
+    lib.call("pyre_gated_norm", _ptr(y), _ptr(parts), n_parts, stride, _ptr(y_bias), _ptr(gate),
+             _ptr(gate_bias) if gate is not None else None, weight.data_ptr(), out.data_ptr(), T, H, float(eps), int(bool(center)),
+             _dt(act_dtype), _stream())
     return out
 
 
@@ -1542,9 +1661,10 @@ def expert_linear(x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, src: 
     return out
 
 
-def route(h: torch.Tensor, w: torch.Tensor, correction: "torch.Tensor | None", top: int, scale: float):
-    """Router of a routed feed-forward: fp32 logits w h over all router outputs, softmax scores s; the ``top``
-    outputs with the largest s + correction are chosen (lowest index on ties), weights s * scale.
+def route(h: torch.Tensor, w: torch.Tensor, correction: "torch.Tensor | None", top: int, scale: float, sigmoid: bool = False):
+    """Router of a routed feed-forward: fp32 logits w h over all router outputs, softmax scores s (``sigmoid``: each
+    output's own sigmoid instead); the ``top`` outputs with the largest s + correction are chosen (lowest index on
+    ties), weights s * scale.
     Returns (idx int32 [T, top], weight fp32 [T, top])."""
     _check(h, "h", dim=2)
     _check(w, "w", torch.float32, 2)
@@ -1561,7 +1681,7 @@ def route(h: torch.Tensor, w: torch.Tensor, correction: "torch.Tensor | None", t
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     weight = torch.empty((T, top), dtype=torch.float32, device=h.device)
     lib.call("pyre_route", h.data_ptr(), w.data_ptr(), _ptr(correction), idx.data_ptr(), weight.data_ptr(), T, H, n_out, int(top),
-             float(scale), _dt(h.dtype), _stream())
+             float(scale), int(bool(sigmoid)), _dt(h.dtype), _stream())
     return idx, weight
 
 
@@ -1592,6 +1712,90 @@ def combine_pairs(y: torch.Tensor, h: torch.Tensor, place_of: torch.Tensor, weig
     out = torch.empty((T, H), dtype=torch.float32, device=h.device)
     lib.call("pyre_combine_pairs", y.data_ptr(), h.data_ptr(), place_of.data_ptr(), weight.data_ptr(), out.data_ptr(), T, H,
              place_of.shape[1], _dt(h.dtype), _stream())
+    return out
+
+
+def scale_to_places(h: torch.Tensor, place_of: torch.Tensor, weight: torch.Tensor, n_places: int) -> torch.Tensor:
+    """out[place_of[t, k]] = weight[t, k] * h[t] for every pair with a place: the experts' inputs of a routed
+    feed-forward whose weights multiply what an expert reads, in the order of the sorted places [n_places, H]."""
+    _check(h, "h", dim=2)
+    _check(place_of, "place_of", torch.int32, 2)
+    _check(weight, "weight", torch.float32, 2)
+    T, H = h.shape
+    if place_of.shape != weight.shape or place_of.shape[0] != T:
+        raise ValueError("h, place_of and weight do not match")
+    out = torch.empty((int(n_places), H), dtype=h.dtype, device=h.device)
+    lib.call("pyre_scale_to_places", h.data_ptr(), place_of.data_ptr(), weight.data_ptr(), out.data_ptr(), T, H, place_of.shape[1],
+             _dt(h.dtype), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------------- time mixing with a matrix state
+WKV_MAX_DIM = 128
+
+
+def wkv_state_floats(n_heads: int, dim: int, width: int) -> int:
+    """Floats of one request's state slot: [n_heads, dim, dim] matrices, then the last token's input [width]."""
+    return n_heads * dim * dim + width
+
+
+def token_shift_mix(h: torch.Tensor, state_layer: torch.Tensor, prev_off: int, slots: torch.Tensor, seq_of_token: torch.Tensor,
+                    cu_seqlens: torch.Tensor, mu: torch.Tensor) -> torch.Tensor:
+    """out[s, t] = h[t] + (prev[t] - h[t]) * mu[s] for each of the blends ``mu`` [S, W] (fp32): prev[t] is the row
+    before t inside an entry of the step, and for an entry's first token the vector kept at ``prev_off`` of the
+    request's slot of ``state_layer`` [slots, floats] (zeros for a new request).  Returns [S, T, W]."""
+    _check(h, "h", dim=2)
+    _check(state_layer, "state_layer", torch.float32, 2)
+    _check(slots, "slots", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _check(mu, "mu", torch.float32, 2)
+    T, W = h.shape
+    if mu.shape[1] != W or prev_off < 0 or prev_off + W > state_layer.shape[1] or seq_of_token.shape[0] != T:
+        raise ValueError("mu, the state or the batch do not match the rows")
+    out = torch.empty((mu.shape[0], T, W), dtype=h.dtype, device=h.device)
+    lib.call("pyre_token_shift_mix", h.data_ptr(), state_layer.data_ptr(), state_layer.shape[1], int(prev_off), slots.data_ptr(),
+             seq_of_token.data_ptr(), cu_seqlens.data_ptr(), mu.data_ptr(), out.data_ptr(), T, W, mu.shape[0], _dt(h.dtype), _stream())
+    return out
+
+
+def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, dlog: torch.Tensor, w0: torch.Tensor,
+             u: torch.Tensor, norm_w: torch.Tensor, state_layer: torch.Tensor, prev_off: int, slots: torch.Tensor,
+             cu_seqlens: torch.Tensor, h: torch.Tensor, n_heads: int, dim: int, eps: float) -> torch.Tensor:
+    """The recurrence of a time-mixing layer with a matrix state per head, token by token in fp32, continuing each
+    request's state: with w = exp(-exp(dlog + w0)) per key channel,
+    o_t = (S + diag(u) k_t v_t^T)^T r_t, then S = diag(w_t) S + k_t v_t^T; each head's o_t is divided by its root mean
+    square (``eps`` inside the root), multiplied by ``norm_w`` and by silu(g).  ``r, k, v, g`` [T, n_heads * dim] in
+    the activation dtype, ``dlog`` fp32.  ``state_layer`` [slots, floats] holds [n_heads, dim, dim] per request and,
+    at ``prev_off``, the last input row ``h`` [T, W] of each entry, which this call leaves there.
+    Returns [T, n_heads * dim] in the activation dtype."""
+    _check(r, "r", dim=2)
+    T, HD = r.shape
+    for t, name in ((k, "k"), (v, "v"), (g, "g")):
+        _check(t, name, r.dtype, 2)
+        if tuple(t.shape) != (T, HD):
+            raise ValueError(f"{name} {tuple(t.shape)} != r {(T, HD)}")
+    _check(dlog, "dlog", torch.float32, 2)
+    _check(h, "h", r.dtype, 2)
+    _check(state_layer, "state_layer", torch.float32, 2)
+    _check(slots, "slots", torch.int32, 1)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    for t, name in ((w0, "w0"), (u, "u"), (norm_w, "norm_w")):
+        _check(t, name, torch.float32, 1)
+        if t.shape[0] != HD:
+            raise ValueError(f"{name} has {t.shape[0]} entries, expected {HD}")
+    W = h.shape[1]
+    n_seqs = cu_seqlens.shape[0] - 1
+    if HD != n_heads * dim or tuple(dlog.shape) != (T, HD) or h.shape[0] != T or slots.shape[0] < n_seqs:
+        raise ValueError("the heads, the decay or the batch do not match")
+    if dim > WKV_MAX_DIM:
+        raise UnsupportedSize(f"heads of {dim}: the recurrence takes up to {WKV_MAX_DIM}")
+    if prev_off < n_heads * dim * dim or prev_off + W > state_layer.shape[1]:
+        raise ValueError("the state slot does not hold the matrices and the input row")
+    out = torch.empty((T, HD), dtype=r.dtype, device=r.device)
+    lib.call("pyre_wkv_scan", r.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), dlog.data_ptr(), w0.data_ptr(), u.data_ptr(),
+             norm_w.data_ptr(), state_layer.data_ptr(), state_layer.shape[1], int(prev_off), slots.data_ptr(), cu_seqlens.data_ptr(),
+             h.data_ptr(), out.data_ptr(), T, n_seqs, n_heads, dim, W, float(eps), _dt(r.dtype), _stream())
     return out
 
 

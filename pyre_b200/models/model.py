@@ -45,6 +45,8 @@ def tensor_table(spec: ModelSpec) -> dict[str, TensorSpec]:
     for i, b in enumerate(blocks):
         table.update(collect_tensors(b, spec.block_prefix.format(i=i)))
     table.update(collect_tensors(tail, spec.tail_prefix))
+    for name, rows in spec.vectors.items():
+        table[name] = TensorSpec((int(rows), int(spec.width)), role="vector", init=("normal", 0.0, 0.05))
     return table
 
 
@@ -57,6 +59,7 @@ class Model:
         self.vocab_size = spec.vocab_size
         self.calls, self.kv_groups, self.state_groups = self._bind_schedule()
         self.loaded = False
+        self.vectors: dict = {}
         self.graph_safe = all(all_graph_safe(p) for p in self.parts())
 
     def parts(self) -> list:
@@ -107,7 +110,8 @@ class Model:
                 st_group = st_specs.index(sspec)
                 st_layer = st_layers[st_group]
                 st_layers[st_group] += 1
-            calls.append(BoundCall(n, call.block, kv_group, kv_layer, call.write, st_group, st_layer, bool(call.add_embedding)))
+            calls.append(BoundCall(n, call.block, kv_group, kv_layer, call.write, st_group, st_layer, bool(call.add_embedding),
+                                   tuple(call.add_vector) if call.add_vector is not None else None))
         kv_groups = [KVGroup(s, n) for s, n in zip(kv_specs, kv_layers)]
         state_groups = [StateGroup(s, n) for s, n in zip(st_specs, st_layers)]
         return calls, kv_groups, state_groups
@@ -125,6 +129,7 @@ class Model:
             for name in [n for n in tensors if n.startswith(prefix)]:
                 del tensors[name]
         load_part(self.tail, tensors, self.spec.tail_prefix)
+        self.vectors = {name: tensors[name] for name in self.spec.vectors}
         self.loaded = True
 
     def load_weights(self, model_dir: "str | Path") -> None:
@@ -137,7 +142,7 @@ class Model:
         self._bind(tensors)
 
     def kernel_libraries(self) -> list[str]:
-        libs = []
+        libs = ["blockops"] if self.spec.vectors else []
         for part in self.parts():
             libs += collect_libraries(part)
         return list(dict.fromkeys(libs + ["sampling"]))
@@ -155,6 +160,10 @@ class Model:
             if call.add_embedding:
                 from ..kernels import ops
                 ops.add_residual(x, fed)      # a branch output still pending is added by the block's norm, as ever
+            if call.add_vector is not None:
+                from ..kernels import ops
+                name, row = call.add_vector
+                ops.add_row_vector(x, self.vectors[name][row])
             x, pending = self.blocks[call.block].forward(ctx, x, pending, call)
         if ctx.num_logit_rows == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32, device=self.device)

@@ -18,12 +18,15 @@ class LayerCall:
     schedule writes them, later ones need ``write=False`` and read them.
     ``add_embedding``: before this entry runs, the embedding's output (the stream as it was before the first
     entry) is added to the stream: a model that runs a span of its layers several times feeds its input in
-    again at the start of every repeat."""
+    again at the start of every repeat.
+    ``add_vector``: (name, row) of one of ``ModelSpec.vectors``: before this entry runs, that row of the tensor is
+    added to every token's stream (a model that marks each repeat of a span with a learned vector)."""
 
     block: int
     cache: "int | str | None" = None
     write: bool = True
     add_embedding: bool = False
+    add_vector: "tuple | None" = None
 
 
 @dataclass
@@ -46,6 +49,10 @@ class ModelSpec:
     max_positions: int = 0
     tail: "PartSpec | None" = None
     tail_prefix: str = ""
+    # checkpoint tensors [rows, width] that belong to no part: a schedule entry adds one of their rows to the stream
+    # (``LayerCall.add_vector``); full checkpoint name -> number of rows
+    vectors: dict = field(default_factory=dict)
+    width: int = 0
 
     def __post_init__(self):
         if not self.schedule:
@@ -53,6 +60,10 @@ class ModelSpec:
         for call in self.schedule:
             if not 0 <= call.block < len(self.blocks):
                 raise ValueError(f"schedule names block {call.block}, the model has {len(self.blocks)}")
+            if call.add_vector is not None:
+                name, row = call.add_vector
+                if name not in self.vectors or not 0 <= row < self.vectors[name] or self.width <= 0:
+                    raise ValueError(f"schedule adds row {row} of {name!r}, which the model's vectors (and width) do not give")
         if self.tail is None:
             if self.final_norm is None or self.head is None:
                 raise ValueError("a model needs a tail: give final_norm and head, or tail")

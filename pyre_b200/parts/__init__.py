@@ -1,4 +1,4 @@
-from . import attention, block, embedding, latent_attention, linear_attention, mlp, norm, rotary  # noqa: F401  (register the built-in parts)
+from . import attention, block, embedding, latent_attention, linear_attention, mlp, norm, rotary, wkv  # noqa: F401  (register the built-in parts)
 from .base import (BoundCall, HeadGeometry, PagedKVSpec, Part, PartSpec, PositionEncoding, ProjectionLayout, StateSpec, all_graph_safe, collect_libraries, collect_tensors,
                    load_part, make_part, register_part, registered_parts)
 

@@ -28,15 +28,20 @@ class Attention(Part):
     holds both, ``ops.attention_row_dim``, the rest zero);
     ``qk_norm``: an RMS norm per head over the ``head_dim`` dims of queries and keys before the position encoding,
     ``{"eps": e}``, with weights of ``head_dim`` entries shared by the heads (names ``q_norm`` / ``k_norm``);
-    ``sink``: the score of a sink that has no value: exp(sink) joins every softmax denominator;
+    ``sink``: the score of a sink that has no value: exp(sink) joins every softmax denominator; ``"learned"``: a score
+    per query head read from the checkpoint (name ``sink``, [n_heads]);
     ``out_gate``: the concatenated heads are multiplied by sigmoid(W_g h) before the output projection (name ``g``);
+    ``"head"``: ONE gate per head (W_g has ``n_heads`` rows);
+    ``value_position``: the PartSpec of a rotation (half-split pairs over all ``v_head_dim`` dims) by which each
+    token's VALUES are turned by the token's own position before they are cached; each head's weighted sum is turned
+    back by the query's position before the gate (the sum then depends on position differences only);
     ``own_kv=False``: the mixer has no key and value projections (and no key norm): it reads the cache layer that
     another entry of the schedule writes (``LayerCall(cache=..., write=False)``);
     ``weight_suffix``: what follows a projection's name in the checkpoint (".weight").
     """
 
     DEFAULT_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "g": "g_proj", "q_norm": "q_norm.weight",
-                     "k_norm": "k_norm.weight"}
+                     "k_norm": "k_norm.weight", "sink": "sink"}
 
     graph_safe = True
     takes_scaled_rows = True      # ``h`` may be ``ops.ScaledRows``: the q/k/v product applies the norm's 1/rms itself
@@ -45,14 +50,23 @@ class Attention(Part):
                  position: "PartSpec | None" = None, qkv_bias: bool = True, o_bias: bool = False,
                  scale: "float | None" = None, window: "int | None" = None, names: "dict[str, str] | None" = None,
                  v_head_dim: "int | None" = None, qk_norm: "dict | None" = None, sink: "float | None" = None,
-                 out_gate: bool = False, own_kv: bool = True, weight_suffix: str = ".weight"):
+                 out_gate: "bool | str" = False, own_kv: bool = True, weight_suffix: str = ".weight",
+                 value_position: "PartSpec | None" = None):
         super().__init__(dtype, device)
         self.v_head_dim = int(v_head_dim) if v_head_dim is not None else int(head_dim)
         self.qk_norm_eps = float(qk_norm["eps"]) if qk_norm is not None else None
-        self.sink = float(sink) if sink is not None else None
+        self.learned_sink = sink == "learned"
+        self.sink = None if sink is None or self.learned_sink else float(sink)
+        if out_gate not in (False, True, "head"):
+            raise ValueError(f"out_gate {out_gate!r}: False, True (a gate per entry) or 'head' (one per head)")
+        self.head_gate = out_gate == "head"
         self.out_gate, self.own_kv, self.suffix = bool(out_gate), bool(own_kv), str(weight_suffix)
+        self.value_position = make_part("position", value_position, dtype, device) if value_position is not None else None
+        if self.value_position is not None and (self.v_head_dim % 2 or getattr(self.value_position, "pairing", "half") != "half"):
+            raise ops.UnsupportedSize("rotated values: an even value size and half-split pairs")
         # the general path: projections laid out by a ProjectionLayout, unfused small kernels
-        self.general = self.v_head_dim != int(head_dim) or qk_norm is not None or self.out_gate or not self.own_kv
+        self.general = (self.v_head_dim != int(head_dim) or qk_norm is not None or self.out_gate or not self.own_kv
+                        or self.value_position is not None or self.learned_sink)
         if self.general and qkv_bias:
             raise ops.UnsupportedSize("projection biases together with v_head_dim, qk_norm, out_gate or own_kv=False are not implemented")
         self.names = dict(self.DEFAULT_NAMES, **(names or {}))
@@ -81,7 +95,7 @@ class Attention(Part):
 
     def children(self):
         # a position encoding with tensors of its own would find them under the mixer's prefix
-        return {"": self.position}
+        return {"": self.position} if self.value_position is None else {"": self.position, "value.": self.value_position}
 
     def tensors(self):
         q, kv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
@@ -99,7 +113,9 @@ class Attention(Part):
                 if self.own_kv:
                     t[n["k_norm"]] = TensorSpec((self.head_dim,), role="vector", init=("normal", 1.0, 0.1))
             if self.out_gate:
-                t[n["g"] + sfx] = TensorSpec((vq, self.width))
+                t[n["g"] + sfx] = TensorSpec((self.n_heads if self.head_gate else vq, self.width))
+            if self.learned_sink:
+                t[n["sink"]] = TensorSpec((self.n_heads,), role="vector", init=("normal", 0.0, 1.0))
             t[n["o"] + sfx] = TensorSpec((self.width, vq))
             return t
         # checkpoint order: weight then bias per projection, the output projection last
@@ -122,6 +138,8 @@ class Attention(Part):
                 self.q_norm_w = tensors[n["q_norm"]]
                 self.k_norm_w = tensors[n["k_norm"]] if self.own_kv else None
             self.w_o = tensors[n["o"] + sfx]
+            if self.learned_sink:
+                self.sink = tensors[n["sink"]]
             return
         self.w_qkv = torch.cat([tensors[f"{n[k]}.weight"] for k in "qkv"], dim=0).contiguous()
         if self.qkv_bias:
@@ -168,10 +186,18 @@ class Attention(Part):
             raise ValueError("a mixer with its own keys and values writes its cache layer; one without reads another's")
         with lib.section("qkv"):
             proj = ops.materialize(ops.linear(h, self.w_proj))
+        kw, vcos, vsin = {}, None, None
+        if self.value_position is not None:
+            vcos, vsin, _ = self.value_position.rotation(ctx, self.v_head_dim)
+            kw["value_tables"] = (vcos, vsin)
         q = self.position.apply_layout(ctx, proj, self.layout, self.q_norm_w, self.k_norm_w, self.qk_norm_eps or 0.0, kv,
-                                       layer if call.kv_write else None)
+                                       layer if call.kv_write else None, **kw)
         a = self._attend(ctx, q, layer, kv)
-        if self.out_gate or self.row_dim != self.v_head_dim:
+        if self.head_gate or vcos is not None:
+            if self.out_gate and not self.head_gate:
+                raise ops.UnsupportedSize("rotated values with a gate per entry are not implemented")
+            a = ops.head_gate(a, self.row_dim, proj if self.head_gate else None, self.g_col, self.n_heads, self.v_head_dim, vcos, vsin)
+        elif self.out_gate or self.row_dim != self.v_head_dim:
             a = ops.sigmoid_gate(a, self.row_dim, proj if self.out_gate else None, self.g_col, self.n_heads, self.v_head_dim)
         with lib.section("o"):
             return ops.linear(a, self.w_o, partials_ok=True)

@@ -148,6 +148,7 @@ class BoundCall:
     state_group: int | None = None
     state_layer: int = 0
     add_embedding: bool = False   # the embedding's output is added to the stream before this entry runs
+    add_vector: "tuple | None" = None   # (tensor name, row): that row is added to every token's stream before the entry
 
 
 class Part:
@@ -199,17 +200,20 @@ class PositionEncoding(Part):
         encoding that does not rotate.  Used by ``apply_layout``."""
         return None, None, 0
 
-    def apply_layout(self, ctx, proj, layout: ProjectionLayout, q_norm, k_norm, norm_eps: float, kv, cache_layer):
+    def apply_layout(self, ctx, proj, layout: ProjectionLayout, q_norm, k_norm, norm_eps: float, kv, cache_layer,
+                     value_tables=None):
         """The same step for projections laid out by a ``ProjectionLayout`` (key and value sizes that differ, rows
         padded to the cache's row size), with an optional RMS norm per head over the query and key dims before
         the encoding (``q_norm`` / ``k_norm``: fp32 weights [qk_dim] or None).  Stores keys and values in
         ``cache_layer`` (None: nothing) and returns the queries [T, n_heads * row_dim].  An encoding that is a
-        rotation of leading dims only has to give ``rotation``."""
+        rotation of leading dims only has to give ``rotation``.  ``value_tables``: (cos, sin) [T, v_dim / 2] of a
+        rotation that the mixer wants on the VALUES before they are cached (given only by a mixer that has one)."""
         from ..kernels import ops
         cos, sin, rotary_dim = self.rotation(ctx, layout.qk_dim)
         return ops.qk_norm_rope_write(proj, layout.q_col, layout.k_col, layout.v_col, q_norm, k_norm, norm_eps, cos, sin,
                                       cache_layer, kv.slot_mapping, layout.n_heads, layout.n_kv_heads, layout.qk_dim,
-                                      layout.v_dim, layout.row_dim, rotary_dim, kv.page_size)
+                                      layout.v_dim, layout.row_dim, rotary_dim, kv.page_size,
+                                      *(value_tables or ()))
 
     @staticmethod
     def store(qkv, bias, heads: HeadGeometry, kv, cache_layer):

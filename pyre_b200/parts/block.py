@@ -169,3 +169,91 @@ class ParallelBlock(Part):
 
 
 register_part("block", "parallel", ParallelBlock)
+
+
+class SandwichBlock(Part):
+    """A norm before AND after each sublayer, and a gate per feature on the sublayer's result:
+
+        h = norm1(x);  x = x + norm1b(mixer(h) * sigmoid(W_g1 h + b_g1))
+        h = norm2(x);  x = x + norm2b(ffn(h)   * sigmoid(W_g2 h + b_g2))
+
+    The gate reads what the sublayer reads and comes before the norm of the sublayer's result.  ``gated=False``: no
+    gates (a plain sandwich of norms).  ``ffn`` None (with ``norm2`` and ``norm2b`` None): the layer has the mixer only.
+
+    The stream ``x`` is fp32.  A sublayer's gated, normed result is formed in fp32 by one kernel (``gated_output`` of
+    the norm part) and travels unadded, as ``pending``, to the next norm before a sublayer, whose kernel adds it to
+    the stream while it normalises.  ``names``: the prefixes of the sub-parts' tensors and the names of the gates'
+    weights and biases."""
+
+    graph_safe = True
+
+    DEFAULT_NAMES = {"norm1": "norm1.", "norm1b": "norm1b.", "mixer": "mixer.", "norm2": "norm2.", "norm2b": "norm2b.",
+                     "ffn": "ffn.", "gate1": "gate1.weight", "gate1_bias": "gate1.bias", "gate2": "gate2.weight",
+                     "gate2_bias": "gate2.bias"}
+
+    def __init__(self, dtype, device, width: int, norm1: PartSpec, mixer: PartSpec, norm1b: PartSpec,
+                 norm2: "PartSpec | None" = None, ffn: "PartSpec | None" = None, norm2b: "PartSpec | None" = None,
+                 gated: bool = True, names: "dict[str, str] | None" = None):
+        super().__init__(dtype, device)
+        if len({norm2 is None, ffn is None, norm2b is None}) != 1:
+            raise ValueError("a second sublayer needs its feed-forward and both of its norms")
+        self.names = dict(self.DEFAULT_NAMES, **(names or {}))
+        self.width, self.gated = int(width), bool(gated)
+        self.norm1 = make_part("norm", norm1, dtype, device)
+        self.mixer = make_part("mixer", mixer, dtype, device)
+        self.norm1b = make_part("norm", norm1b, dtype, device)
+        self.norm2 = make_part("norm", norm2, dtype, device) if norm2 is not None else None
+        self.ffn = make_part("ffn", ffn, dtype, device) if ffn is not None else None
+        self.norm2b = make_part("norm", norm2b, dtype, device) if norm2b is not None else None
+        for n in (self.norm1b, self.norm2b):
+            if n is not None and not hasattr(n, "gated_output"):
+                raise ValueError(f"{type(n).__name__} cannot sit on a sublayer's result: it has no gated_output")
+        self.w_g1 = self.b_g1 = self.w_g2 = self.b_g2 = None
+
+    def children(self):
+        n = self.names
+        out = {n["norm1"]: self.norm1, n["mixer"]: self.mixer, n["norm1b"]: self.norm1b}
+        if self.ffn is not None:
+            out.update({n["norm2"]: self.norm2, n["ffn"]: self.ffn, n["norm2b"]: self.norm2b})
+        return out
+
+    def tensors(self):
+        from ..weights.specs import TensorSpec
+        if not self.gated:
+            return {}
+        n, W = self.names, self.width
+        t = {n["gate1"]: TensorSpec((W, W)), n["gate1_bias"]: TensorSpec((W,), role="vector")}
+        if self.ffn is not None:
+            t.update({n["gate2"]: TensorSpec((W, W)), n["gate2_bias"]: TensorSpec((W,), role="vector")})
+        return t
+
+    def load(self, tensors):
+        if not self.gated:
+            return
+        n = self.names
+        self.w_g1, self.b_g1 = tensors[n["gate1"]], tensors[n["gate1_bias"]]
+        if self.ffn is not None:
+            self.w_g2, self.b_g2 = tensors[n["gate2"]], tensors[n["gate2_bias"]]
+
+    def kernel_libraries(self):
+        import torch
+        return ["blockops"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"])
+
+    def _sublayer(self, ctx, h, branch, w_gate, b_gate, norm_b):
+        from ..kernels import lib, ops
+        gate = None
+        if self.gated:
+            with lib.section("residual_gate"):
+                gate = ops.materialize(ops.linear(h, w_gate))
+        return norm_b.gated_output(ctx, branch, gate, b_gate)
+
+    def forward(self, ctx, x, pending, call):
+        h = self.norm1.forward(ctx, x, delta=pending)
+        pending = self._sublayer(ctx, h, self.mixer.forward(ctx, h, call), self.w_g1, self.b_g1, self.norm1b)
+        if self.ffn is not None:
+            h = self.norm2.forward(ctx, x, delta=pending)
+            pending = self._sublayer(ctx, h, self.ffn.forward(ctx, h), self.w_g2, self.b_g2, self.norm2b)
+        return x, pending
+
+
+register_part("block", "sandwich", SandwichBlock)

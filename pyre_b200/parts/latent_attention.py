@@ -25,33 +25,37 @@ class LatentAttention(Part):
     q~_n = U_k,n^T q_plain,n (a product per head), scores against the cached rows themselves, the weighted sum of
     the latents per head, and then the head's value map (a second product per head).  Keys and values are never
     expanded, in prompts or in decoding.  ``window``: a query at position p sees p - window + 1 .. p (None: all).
-    ``position``: the PartSpec of a rotation that gives tables (``rotation(ctx, rope_dim)``) and pairs neighbours.
-    Norms, angles, scores and the softmax are fp32."""
+    ``position``: the PartSpec of a rotation that gives tables (``rotation(ctx, rope_dim)``) and pairs neighbours
+    (None with ``rope_dim`` 0: attention without positions).  ``q_rank`` None: the queries have no latent of their own,
+    q = W_q h (name ``q``).  Norms, angles, scores and the softmax are fp32."""
 
     DEFAULT_NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk",
-                     "uv": "uv", "o": "o"}
+                     "uv": "uv", "o": "o", "q": "q"}
 
     graph_safe = True
 
-    def __init__(self, dtype, device, width: int, n_heads: int, head_dim: int, rope_dim: int, v_head_dim: int, q_rank: int,
-                 kv_rank: int, scale: float, eps: float, position: PartSpec, window: "int | None" = None,
-                 names: "dict[str, str] | None" = None):
+    def __init__(self, dtype, device, width: int, n_heads: int, head_dim: int, rope_dim: int, v_head_dim: int,
+                 q_rank: "int | None", kv_rank: int, scale: float, eps: float, position: "PartSpec | None" = None,
+                 window: "int | None" = None, names: "dict[str, str] | None" = None):
         super().__init__(dtype, device)
         self.names = dict(self.DEFAULT_NAMES, **(names or {}))
         self.width, self.n_heads, self.head_dim, self.rope_dim = int(width), int(n_heads), int(head_dim), int(rope_dim)
-        self.v_head_dim, self.q_rank, self.kv_rank = int(v_head_dim), int(q_rank), int(kv_rank)
+        self.v_head_dim, self.q_rank, self.kv_rank = int(v_head_dim), int(q_rank) if q_rank is not None else 0, int(kv_rank)
+        self.q_latent = q_rank is not None
         self.scale, self.eps = float(scale), float(eps)
         if window is not None and window <= 0:
             raise ValueError("window must be positive or None")
         self.window = window
-        if min(self.n_heads, self.head_dim, self.v_head_dim, self.q_rank, self.kv_rank) <= 0 or self.rope_dim < 0:
+        if min(self.n_heads, self.head_dim, self.v_head_dim, self.q_rank if self.q_latent else 1, self.kv_rank) <= 0 or self.rope_dim < 0:
             raise ValueError("the sizes of a latent attention are positive")
         if self.kv_rank > ops.LATENT_MAX_RANK:
             raise ops.UnsupportedSize(f"kv_rank {kv_rank}: the latent attention kernels take up to {ops.LATENT_MAX_RANK}")
         # a cache row: latent, rotated key part, zeros up to a multiple of 16 entries (whole k-steps of the MMA)
         self.row = -(-(self.kv_rank + self.rope_dim) // 16) * 16
-        self.position = make_part("position", position, dtype, device)
-        if getattr(self.position, "pairing", "interleaved") != "interleaved":
+        if position is None and self.rope_dim:
+            raise ValueError("a rotated key part needs a position encoding")
+        self.position = make_part("position", position or PartSpec("none"), dtype, device)
+        if self.rope_dim and getattr(self.position, "pairing", "interleaved") != "interleaved":
             raise ops.UnsupportedSize("the latent attention kernels rotate neighbouring pairs")
         self.w_down = self.w_uq = self.w_uk_t = self.w_uv = self.w_o = self.g_q = self.g_c = None
 
@@ -60,10 +64,13 @@ class LatentAttention(Part):
 
     def tensors(self):
         n, H = self.names, self.n_heads
-        return {
+        queries = {
             n["dq"]: TensorSpec((self.q_rank, self.width)),
             n["dq_norm"]: TensorSpec((self.q_rank,), role="vector", init=("normal", 1.0, 0.1)),
             n["uq"]: TensorSpec((H * (self.head_dim + self.rope_dim), self.q_rank)),
+        } if self.q_latent else {n["q"]: TensorSpec((H * (self.head_dim + self.rope_dim), self.width))}
+        return {
+            **queries,
             n["dkv"]: TensorSpec((self.kv_rank + self.rope_dim, self.width)),
             n["dkv_norm"]: TensorSpec((self.kv_rank,), role="vector", init=("normal", 1.0, 0.1)),
             n["uk"]: TensorSpec((H * self.head_dim, self.kv_rank)),
@@ -73,14 +80,17 @@ class LatentAttention(Part):
 
     def load(self, tensors):
         n, H = self.names, self.n_heads
-        self.w_down = torch.cat([tensors[n["dq"]], tensors[n["dkv"]]], dim=0).contiguous()
-        self.w_uq = tensors[n["uq"]]
+        if self.q_latent:
+            self.w_down = torch.cat([tensors[n["dq"]], tensors[n["dkv"]]], dim=0).contiguous()
+            self.w_uq, self.g_q = tensors[n["uq"]], tensors[n["dq_norm"]]
+        else:
+            self.w_down, self.w_uq = tensors[n["dkv"]], tensors[n["q"]]
         # the key map moves to the query: per head [kv_rank, head_dim], the layout of a linear layer from
         # head_dim to kv_rank
         self.w_uk_t = tensors[n["uk"]].view(H, self.head_dim, self.kv_rank).transpose(1, 2).contiguous()
         self.w_uv = tensors[n["uv"]].view(H, self.v_head_dim, self.kv_rank).contiguous()
         self.w_o = tensors[n["o"]]
-        self.g_q, self.g_c = tensors[n["dq_norm"]], tensors[n["dkv_norm"]]
+        self.g_c = tensors[n["dkv_norm"]]
 
     def kernel_libraries(self):
         return ["latent_attention", "grouped", "elementwise"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"])
@@ -109,11 +119,12 @@ class LatentAttention(Part):
         cq = ops.latent_prepare(down, 0, self.q_rank, self.q_rank, self.kv_rank, self.rope_dim, rot, self.g_q, self.g_c,
                                 self.eps, cos, sin, layer if call.kv_write else None, kv.slot_mapping, kv.page_size, self.dtype)
         with lib.section("q_up"):
-            q = ops.materialize(ops.linear(cq, self.w_uq))
+            q = ops.materialize(ops.linear(cq if self.q_latent else h, self.w_uq))
         qa = torch.empty((T, H, self.row), dtype=self.dtype, device=q.device)
         with lib.section("absorb"):
             ops.headwise_linear(q.view(T, H, self.head_dim + self.rope_dim), self.w_uk_t, out=qa)
-        ops.latent_rotate_q(q, qa, cos, sin, H, self.head_dim, self.rope_dim, rot, self.kv_rank)
+        if self.row > self.kv_rank:      # the rotated tail of the rows, and zeros up to the row size
+            ops.latent_rotate_q(q, qa, cos, sin, H, self.head_dim, self.rope_dim, rot, self.kv_rank)
         lat = ops.latent_attention(ctx, qa, layer, kv.block_table, self.kv_rank, self.rope_dim, self.scale, self.window)
         with lib.section("v_up"):
             heads = ops.headwise_linear(lat, self.w_uv)

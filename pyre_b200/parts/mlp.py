@@ -6,7 +6,7 @@ import torch
 
 from ..kernels import lib, ops
 from ..weights.specs import TensorSpec
-from .base import Part, register_part
+from .base import Part, PartSpec, make_part, register_part
 
 
 class GatedMLP(Part):
@@ -73,39 +73,51 @@ register_part("ffn", "gated_mlp", GatedMLP)
 
 
 class DenseMLP(Part):
-    """down(act(up(h))) without biases: a feed-forward with one product before the activation.
-    ``activation``: ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))) or ``silu``, computed in fp32
-    on the product's result.  ``names``: the checkpoint's full local names of the two weights."""
+    """down(act(up(h))): a feed-forward with one product before the activation.
+    ``activation``: ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))), ``silu`` or ``relu2`` (the
+    square of relu), computed in fp32 on the product's result.  ``bias``: both projections have one (names ``up_bias``
+    / ``down_bias``); the first is added before the activation, the second to the result.  ``names``: the
+    checkpoint's full local names of the tensors."""
 
-    DEFAULT_NAMES = {"up": "up_proj.weight", "down": "down_proj.weight"}
+    DEFAULT_NAMES = {"up": "up_proj.weight", "down": "down_proj.weight", "up_bias": "up_proj.bias", "down_bias": "down_proj.bias"}
 
     graph_safe = True
 
     def __init__(self, dtype, device, width: int, intermediate: int, activation: str = "gelu_tanh",
-                 names: "dict[str, str] | None" = None):
+                 names: "dict[str, str] | None" = None, bias: bool = False):
         super().__init__(dtype, device)
         self.names = dict(self.DEFAULT_NAMES, **(names or {}))
-        self.width, self.intermediate = int(width), int(intermediate)
-        if activation not in ops.ACTIVATIONS:
-            raise ops.UnsupportedSize(f"activation {activation!r}: implemented are {sorted(ops.ACTIVATIONS)}")
+        self.width, self.intermediate, self.bias = int(width), int(intermediate), bool(bias)
+        if activation not in ops.BIAS_ACTIVATIONS or activation is None:
+            raise ops.UnsupportedSize(f"activation {activation!r}: implemented are {sorted(k for k in ops.BIAS_ACTIVATIONS if k)}")
         self.activation = activation
-        self.w_up = self.w_down = None
+        self.w_up = self.w_down = self.b_up = self.b_down = None
 
     def tensors(self):
-        return {self.names["up"]: TensorSpec((self.intermediate, self.width)),
-                self.names["down"]: TensorSpec((self.width, self.intermediate))}
+        t = {self.names["up"]: TensorSpec((self.intermediate, self.width)),
+             self.names["down"]: TensorSpec((self.width, self.intermediate))}
+        if self.bias:
+            t[self.names["up_bias"]] = TensorSpec((self.intermediate,), role="vector")
+            t[self.names["down_bias"]] = TensorSpec((self.width,), role="vector")
+        return t
 
     def load(self, tensors):
         self.w_up, self.w_down = tensors[self.names["up"]], tensors[self.names["down"]]
+        if self.bias:
+            self.b_up, self.b_down = tensors[self.names["up_bias"]], tensors[self.names["down_bias"]]
 
     def kernel_libraries(self):
         return ["blockops", "elementwise"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"])
 
     def forward(self, ctx, h):
         with lib.section("up"):
-            a = ops.linear_act(h, self.w_up, self.activation)
+            if self.bias or self.activation not in ops.ACTIVATIONS:
+                a = ops.bias_act(ops.materialize(ops.linear(h, self.w_up)), self.b_up, self.activation)
+            else:
+                a = ops.linear_act(h, self.w_up, self.activation)
         with lib.section("down"):
-            return ops.linear(a, self.w_down, partials_ok=True)
+            y = ops.linear(a, self.w_down, partials_ok=not self.bias)
+            return ops.bias_act(ops.materialize(y), self.b_down, None) if self.bias else y
 
 
 register_part("ffn", "dense_mlp", DenseMLP)
@@ -117,19 +129,31 @@ class RoutedMLP(Part):
     of them.  The router's logits W_r h are fp32, the scores a softmax over ALL router outputs; the choice takes
     the ``top`` largest of score + correction (a tensor per router output, ``correction=True``), the weights are the
     chosen outputs' plain scores times ``scale``, not renormalised.  The result is the weighted sum.
+    ``scores="sigmoid"``: each router output's score is its own sigmoid instead of the softmax over all.
+    ``weight_on="input"``: the weight multiplies what the expert READS (the result is the plain sum of
+    expert(weight * h); needs ``n_identity`` 0); ``"output"``: what it returns.
+    ``shared``: the intermediate size of one more gated feed-forward of the same form that runs for every token and
+    is added (names under ``shared``), or None.
 
     On the device throughout (no host reads): the router kernel, a sort of the (token, choice) pairs by expert,
     two products with one weight matrix per expert over the sorted pairs with the activation between them, and the
     weighted sum per token in fp32.  ``names``: the prefix of expert e's tensors (``expert``, formatted with e), the
     local names of its three projections, the router's and the correction's names."""
 
-    DEFAULT_NAMES = {"expert": "e{e}.", "gate": "gate", "up": "up", "down": "down", "router": "router", "correction": "correction"}
+    DEFAULT_NAMES = {"expert": "e{e}.", "gate": "gate", "up": "up", "down": "down", "router": "router", "correction": "correction",
+                     "shared": "shared."}
 
     graph_safe = True
 
     def __init__(self, dtype, device, width: int, intermediate: int, n_experts: int, top: int, scale: float = 1.0,
-                 n_identity: int = 0, activation: str = "silu", correction: bool = True, names: "dict[str, str] | None" = None):
+                 n_identity: int = 0, activation: str = "silu", correction: bool = True, names: "dict[str, str] | None" = None,
+                 scores: str = "softmax", weight_on: str = "output", shared: "int | None" = None):
         super().__init__(dtype, device)
+        if scores not in ("softmax", "sigmoid") or weight_on not in ("output", "input"):
+            raise ValueError(f"router scores {scores!r} / weight_on {weight_on!r}: 'softmax' or 'sigmoid', 'output' or 'input'")
+        if weight_on == "input" and n_identity:
+            raise ValueError("weights on the experts' inputs and router outputs without weights do not go together")
+        self.sigmoid, self.weight_on_input = scores == "sigmoid", weight_on == "input"
         self.names = dict(self.DEFAULT_NAMES, **(names or {}))
         self.width, self.intermediate = int(width), int(intermediate)
         self.n_experts, self.n_identity, self.top, self.scale = int(n_experts), int(n_identity), int(top), float(scale)
@@ -138,7 +162,14 @@ class RoutedMLP(Part):
         if self.n_experts <= 0 or self.n_identity < 0 or not 0 < self.top <= self.n_experts + self.n_identity:
             raise ValueError(f"a routed feed-forward of {n_experts} + {n_identity} experts cannot choose {top}")
         self.activation, self.has_correction = activation, bool(correction)
-        self.w_gate_up = self.w_down = self.w_router = self.correction = None
+        self.w_gate_up = self.w_down = self.w_router = self.correction = self._ones = None
+        n = self.names
+        self.shared = make_part("ffn", PartSpec("gated_mlp", {
+            "width": self.width, "intermediate": int(shared), "activation": activation, "weight_suffix": "",
+            "names": {"gate": n["gate"], "up": n["up"], "down": n["down"]}}), dtype, device) if shared else None
+
+    def children(self):
+        return {self.names["shared"]: self.shared} if self.shared is not None else {}
 
     def tensors(self):
         n, t = self.names, {}
@@ -167,15 +198,22 @@ class RoutedMLP(Part):
     def forward(self, ctx, h):
         h = ops.materialize(h)
         T = h.shape[0]
-        idx, weight = ops.route(h, self.w_router, self.correction, self.top, self.scale)
+        idx, weight = ops.route(h, self.w_router, self.correction, self.top, self.scale, sigmoid=self.sigmoid)
         offsets, place_of, src = ops.group_pairs(idx, self.n_experts)
         places = T * self.top
+        x = h
+        if self.weight_on_input:
+            # the experts read weight * h, laid out by place; their results are summed unweighted
+            x, src = ops.scale_to_places(h, place_of, weight, places), None
+            weight = torch.ones_like(weight)
         with lib.section("experts_gate_up"):
-            gu = ops.expert_linear(h, self.w_gate_up, offsets, src, places)
+            gu = ops.expert_linear(x, self.w_gate_up, offsets, src, places)
         act = ops.act_mul(gu, self.activation)
         with lib.section("experts_down"):
             y = ops.expert_linear(act, self.w_down, offsets, None, places, out_dtype=torch.float32)
         out = ops.combine_pairs(y, h, place_of, weight)
+        if self.shared is not None:
+            ops.add_residual(out, ops.materialize(self.shared.forward(ctx, h)))
         # fp32 [T, width]: in bfloat16 it travels as the one part of a split product, which every norm adds unrounded
         return out if self.dtype == torch.float32 else ops.PartialSums(out.unsqueeze(0), self.dtype)
 

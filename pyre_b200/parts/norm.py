@@ -45,6 +45,12 @@ class RMSNorm(Part):
         back as activations for the branch that reads it next."""
         return ops.norm_add(x, y, self.weight, self.eps, self.dtype, want_next=want_next)
 
+    def gated_output(self, ctx, y, gate=None, gate_bias=None):
+        """norm(y * sigmoid(gate + gate_bias)) * gain for a sublayer's result ``y`` that is not added to the stream
+        here: it comes back as an fp32 branch output (one unrounded part in bfloat16) for the next norm to add."""
+        out = ops.gated_norm(y, None, gate, gate_bias, self.weight, self.eps, self.dtype, center=False)
+        return out if self.dtype == torch.float32 else ops.PartialSums(out.unsqueeze(0), self.dtype)
+
 
 register_part("norm", "rms_norm", RMSNorm)
 
@@ -76,6 +82,12 @@ class LayerNorm(Part):
 
     def forward(self, ctx, x, delta=None, rows=None, update_x=True, scaled_ok=False):
         return ops.add_layernorm(x, delta, self.weight, self.eps, self.dtype, rows=rows, update_x=update_x)
+
+    def gated_output(self, ctx, y, gate=None, gate_bias=None):
+        """norm(y * sigmoid(gate + gate_bias)) * gain for a sublayer's result ``y`` that is not added to the stream
+        here: it comes back as an fp32 branch output (one unrounded part in bfloat16) for the next norm to add."""
+        out = ops.gated_norm(y, None, gate, gate_bias, self.weight, self.eps, self.dtype, center=True)
+        return out if self.dtype == torch.float32 else ops.PartialSums(out.unsqueeze(0), self.dtype)
 
     def normalize_stream(self, ctx, x):
         return ops.add_layernorm(x, None, self.weight, self.eps, torch.float32, act_dtype=self.dtype)

@@ -3,6 +3,8 @@ configuration, angles in fp32."""
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..kernels import ops
@@ -14,12 +16,17 @@ class Rotary(PositionEncoding):
     reference's fp32 expression (pyre/model.py:45-47), or in 64-bit rounded once (``exact_frequencies``); per step, cos and sin of
     float(position) * inv_freq for the step's tokens, shared by all layers that have
     the same settings.  ``rotary_dim`` < head_dim rotates only the first dims of a head.  Bias, rotation of
-    q and k and the paged write of k and v are one kernel (``ops.qkv_rope_write``)."""
+    q and k and the paged write of k and v are one kernel (``ops.qkv_rope_write``).
+
+    ``scaling``: ``{"factor", "low", "high", "original"}`` stretches the slow frequencies for contexts beyond the
+    ``original`` length: with the wavelength l = 2 pi / f, a frequency stays where l < original / high, becomes
+    f / factor where l > original / low, and between the two is the blend (1 - s) f / factor + s f with
+    s = (original / l - low) / (high - low).  Computed once, in 64-bit."""
 
     graph_safe = True
 
     def __init__(self, dtype, device, head_dim: int, theta: float, rotary_dim: "int | None" = None,
-                 pairing: str = "half", exact_frequencies: bool = False):
+                 pairing: str = "half", exact_frequencies: bool = False, scaling: "dict | None" = None):
         super().__init__(dtype, device)
         self.head_dim = int(head_dim)
         self.rotary_dim = int(rotary_dim if rotary_dim is not None else head_dim)
@@ -37,8 +44,22 @@ class Rotary(PositionEncoding):
             inv = (self.theta ** (-torch.arange(0, self.rotary_dim, 2, dtype=torch.float64) / self.rotary_dim)).float()
         else:
             inv = 1.0 / (self.theta ** (torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim))
+        self.scaling = None
+        if scaling:
+            try:
+                fac, lo, hi, orig = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+            except KeyError as e:
+                raise ValueError(f"rotary scaling needs factor, low, high and original; {e.args[0]!r} is missing") from None
+            if not (fac > 0 and hi > lo and orig > 0):
+                raise ValueError(f"rotary scaling {scaling!r}: factor and original are positive, high is above low")
+            self.scaling = (fac, lo, hi, orig)
+            f = inv.double() if not exact_frequencies else self.theta ** (-torch.arange(0, self.rotary_dim, 2, dtype=torch.float64) / self.rotary_dim)
+            wave = 2.0 * math.pi / f
+            s = (orig / wave - lo) / (hi - lo)
+            blend = (1.0 - s) * f / fac + s * f
+            inv = torch.where(wave > orig / lo, f / fac, torch.where(wave < orig / hi, f, blend)).float()
         self.inv_freq = inv.to(self.device)
-        self._key = ("rotary", self.rotary_dim, self.theta, bool(exact_frequencies))
+        self._key = ("rotary", self.rotary_dim, self.theta, bool(exact_frequencies), self.scaling)
 
     def kernel_libraries(self):
         return ["elementwise"]
@@ -57,10 +78,10 @@ class Rotary(PositionEncoding):
         cos, sin = self.tables(ctx)
         return cos, sin, self.rotary_dim
 
-    def apply_layout(self, ctx, proj, layout, q_norm, k_norm, norm_eps, kv, cache_layer):
+    def apply_layout(self, ctx, proj, layout, q_norm, k_norm, norm_eps, kv, cache_layer, **kw):
         if self.pairing != "half":
             raise ops.UnsupportedSize("the q/k/v kernels rotate half-split pairs only")
-        return super().apply_layout(ctx, proj, layout, q_norm, k_norm, norm_eps, kv, cache_layer)
+        return super().apply_layout(ctx, proj, layout, q_norm, k_norm, norm_eps, kv, cache_layer, **kw)
 
     def apply(self, ctx, qkv, bias, heads: HeadGeometry, kv, cache_layer):
         if self.pairing != "half":

@@ -87,6 +87,16 @@ def check_names_and_shapes(expected: Mapping[str, TensorSpec], found: Mapping[st
     raise WeightsError("\n".join(lines), missing, unexpected, wrong)
 
 
+def tensor_shapes(model_dir: "str | Path") -> dict[str, tuple[int, ...]]:
+    """name -> shape of every tensor in the model folder's safetensors files (headers only)."""
+    out: dict[str, tuple[int, ...]] = {}
+    for shard in find_shards(model_dir):
+        with safe_open(str(shard), framework="pt", device="cpu") as f:
+            for name in f.keys():
+                out[name] = tuple(f.get_slice(name).get_shape())
+    return out
+
+
 def load_tensors(model_dir: str | Path, expected: Mapping[str, TensorSpec], compute: torch.dtype,
                  device: "str | torch.device", sink: Callable[[str, torch.Tensor], None] | None = None
                  ) -> dict[str, torch.Tensor]:
