@@ -182,12 +182,16 @@ def router_scores(h, w, prefix):
     return torch.sigmoid(h @ w[prefix + "router"].to(F64).T)
 
 
-def moe_mlp(h, w, prefix, mlp, lowp=False):
+def moe_mlp(h, w, prefix, mlp, lowp=False, margins=None):
     """Each token's ``top`` experts by sigmoid score; the score multiplies the expert's INPUT; a shared expert runs
-    for every token."""
+    for every token.  ``margins`` (a list) receives, per token, the gap between the last chosen score and the first
+    one left out."""
     scores = router_scores(_r(h, lowp), w, prefix)
     top = int(mlp["router"]["top"])
     choice = scores.topk(top, dim=-1).indices
+    if margins is not None and top < scores.shape[-1]:
+        ranked = scores.sort(dim=-1, descending=True).values
+        margins.extend((ranked[:, top - 1] - ranked[:, top]).tolist())
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e in choice[t].tolist():
@@ -210,7 +214,7 @@ def layer_order(config):
     return order + [(i, None) for i in range(stop, n)]
 
 
-def forward(config, w, tokens, lowp=False, keep_layers=False):
+def forward(config, w, tokens, lowp=False, keep_layers=False, margins=None):
     """Logits [T, vocab] of one sequence from position 0 (and, with ``keep_layers``, the stream after every layer run)."""
     eps = float(config["norm"]["eps"])
     x = w["embed"].to(F64)[torch.as_tensor(tokens, dtype=torch.long)]
@@ -234,7 +238,7 @@ def forward(config, w, tokens, lowp=False, keep_layers=False):
         mlp = L.get("mlp")
         if mlp:
             h = _r(layer_norm(x, w[p + "norm2"], eps), lowp)
-            f = dense_mlp(h, w, p + "mlp.", lowp) if mlp.get("kind", "dense") == "dense" else moe_mlp(h, w, p + "mlp.", mlp, lowp)
+            f = dense_mlp(h, w, p + "mlp.", lowp) if mlp.get("kind", "dense") == "dense" else moe_mlp(h, w, p + "mlp.", mlp, lowp, margins)
             f = f * torch.sigmoid(matmul(h, w[p + "rg2"], lowp, bias=w[p + "rg2.b"]))
             x = x + layer_norm(f, w[p + "norm2b"], eps)
         if keep_layers:

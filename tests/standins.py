@@ -79,10 +79,11 @@ def paged_attention_generic(q, cache_layer, block_table, seq_of_token, positions
         scores = torch.einsum("grd,kgd->grk", qt, keys) * scale
         if sink is None:
             probs = torch.softmax(scores, dim=-1)
-        else:       # one more term in the denominator, with no value
-            top = scores.max(dim=-1, keepdim=True).values.clamp_min(sink)
+        else:       # one more term in the denominator, with no value; a tensor holds a score per query head
+            sk = sink.float().reshape(n_kv_heads, n_rep, 1) if isinstance(sink, torch.Tensor) else torch.full((1, 1, 1), float(sink))
+            top = torch.maximum(scores.max(dim=-1, keepdim=True).values, sk)
             e = torch.exp(scores - top)
-            probs = e / (e.sum(dim=-1, keepdim=True) + torch.exp(sink - top))
+            probs = e / (e.sum(dim=-1, keepdim=True) + torch.exp(sk - top))
         result[t] = torch.einsum("grk,kgd->grd", probs, vals).reshape(-1).to(q.dtype)
     return result
 
@@ -113,7 +114,7 @@ def linear_act(x, w, kind):
 
 
 def qk_norm_rope_write(proj, q_col, k_col, v_col, q_weight, k_weight, eps, cos, sin, cache_layer, slot_mapping, n_heads,
-                       n_kv_heads, qk_dim, v_dim, row_dim, rotary_dim, page_size):
+                       n_kv_heads, qk_dim, v_dim, row_dim, rotary_dim, page_size, v_cos=None, v_sin=None):
     T = proj.shape[0]
     x = proj.float()
 
@@ -131,7 +132,12 @@ def qk_norm_rope_write(proj, q_col, k_col, v_col, q_weight, k_weight, eps, cos, 
     q = heads(q_col, n_heads, qk_dim, q_weight)
     if cache_layer is not None:
         k = heads(k_col, n_kv_heads, qk_dim, k_weight)
-        v = torch.nn.functional.pad(x[:, v_col:v_col + n_kv_heads * v_dim].reshape(T, n_kv_heads, v_dim), (0, row_dim - v_dim))
+        v = x[:, v_col:v_col + n_kv_heads * v_dim].reshape(T, n_kv_heads, v_dim)
+        if v_cos is not None:      # the values turn over all their dims, by tables of their own
+            a, b = v[..., :v_dim // 2], v[..., v_dim // 2:]
+            c, sn = v_cos[:, None, :], v_sin[:, None, :]
+            v = torch.cat([a * c - b * sn, b * c + a * sn], dim=-1)
+        v = torch.nn.functional.pad(v, (0, row_dim - v_dim))
         for t in range(T):
             page, off = divmod(int(slot_mapping[t]), page_size)
             cache_layer[page, 0, :, off, :] = k[t].to(cache_layer.dtype)
@@ -145,6 +151,81 @@ def sigmoid_gate(a, a_dim, proj, g_col, n_heads, v_dim):
     if proj is not None:
         out = out * torch.sigmoid(proj[:, g_col:g_col + n_heads * v_dim].float())
     return out.to(a.dtype)
+
+
+def head_gate(a, a_dim, proj, g_col, n_heads, v_dim, cos=None, sin=None):
+    T = a.shape[0]
+    out = a.float().reshape(T, n_heads, a_dim)[..., :v_dim]
+    if cos is not None:      # turned back: minus the token's angles
+        x, y = out[..., :v_dim // 2], out[..., v_dim // 2:]
+        c, sn = cos[:, None, :], sin[:, None, :]
+        out = torch.cat([x * c + y * sn, y * c - x * sn], dim=-1)
+    if proj is not None:
+        out = out * torch.sigmoid(proj[:, g_col:g_col + n_heads].float())[:, :, None]
+    return out.reshape(T, n_heads * v_dim).to(a.dtype)
+
+
+def bias_act(x, bias, kind):
+    z = x.float() if bias is None else x.float() + bias
+    fn = {"silu": torch.nn.functional.silu, "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh"),
+          "relu2": lambda t: torch.relu(t) ** 2, "tanh": torch.tanh, None: lambda t: t}[kind]
+    return fn(z).to(x.dtype)
+
+
+def add_row_vector(x, v):
+    x.add_(v)
+    return x
+
+
+def gated_norm(y, y_bias, gate, gate_bias, weight, eps, act_dtype, center=True):
+    v = _partial_sums_or_tensor(y)
+    if y_bias is not None:
+        v = v + y_bias
+    if gate is not None:
+        v = v * torch.sigmoid(gate.float() + (gate_bias if gate_bias is not None else 0.0))
+    if center:
+        v = v - v.mean(-1, keepdim=True)
+    return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight
+
+
+def scale_to_places(h, place_of, weight, n_places):
+    out = torch.full((n_places, h.shape[1]), float("nan"), dtype=h.dtype)
+    for t in range(h.shape[0]):
+        for k in range(place_of.shape[1]):
+            if int(place_of[t, k]) >= 0:
+                out[int(place_of[t, k])] = (weight[t, k] * h[t].float()).to(h.dtype)
+    return out
+
+
+def token_shift_mix(h, state_layer, prev_off, slots, seq_of_token, cu_seqlens, mu):
+    T, W = h.shape
+    x = h.float()
+    prev = torch.empty_like(x)
+    for t in range(T):
+        b = int(seq_of_token[t])
+        prev[t] = state_layer[int(slots[b]), prev_off:prev_off + W] if t == int(cu_seqlens[b]) else x[t - 1]
+    return (x[None] + (prev - x)[None] * mu[:, None, :]).to(h.dtype)
+
+
+def wkv_scan(r, k, v, g, dlog, w0, u, norm_w, state_layer, prev_off, slots, cu_seqlens, h, n_heads, dim, eps):
+    T = r.shape[0]
+    shape = (T, n_heads, dim)
+    rf, kf, vf = r.float().reshape(shape), k.float().reshape(shape), v.float().reshape(shape)
+    decay = torch.exp(-torch.exp(dlog + w0)).reshape(shape)
+    bonus = u.reshape(n_heads, dim)
+    out = torch.empty(shape)
+    for b in range(cu_seqlens.shape[0] - 1):
+        slot = int(slots[b])
+        S = state_layer[slot, :prev_off].reshape(n_heads, dim, dim).clone()
+        for t in range(int(cu_seqlens[b]), int(cu_seqlens[b + 1])):
+            kv = kf[t][:, :, None] * vf[t][:, None, :]
+            out[t] = torch.einsum("hi,hij->hj", rf[t], S + bonus[:, :, None] * kv)
+            S = decay[t][:, :, None] * S + kv
+        state_layer[slot, :prev_off] = S.reshape(-1)
+        if int(cu_seqlens[b + 1]) > int(cu_seqlens[b]):
+            state_layer[slot, prev_off:prev_off + h.shape[1]] = h[int(cu_seqlens[b + 1]) - 1].float()
+    out = out * torch.rsqrt(out.pow(2).mean(-1, keepdim=True) + eps)
+    return (out.reshape(T, -1) * norm_w * torch.nn.functional.silu(g.float())).to(r.dtype)
 
 
 def rmsnorm_gate(o, weight, eps, proj, g_col, out_dtype):
@@ -287,8 +368,8 @@ def headwise_linear(x, w, out=None):
     return out
 
 
-def route(h, w, correction, top, scale):
-    s = torch.softmax(h.float() @ w.t(), dim=-1)
+def route(h, w, correction, top, scale, sigmoid=False):
+    s = torch.sigmoid(h.float() @ w.t()) if sigmoid else torch.softmax(h.float() @ w.t(), dim=-1)
     choice = s if correction is None else s + correction
     idx = choice.topk(top, dim=-1).indices
     return idx.to(torch.int32), s.gather(-1, idx) * scale
@@ -342,7 +423,9 @@ def install(monkeypatch) -> None:
                          sigmoid_gate=sigmoid_gate, rmsnorm_gate=rmsnorm_gate, linear_attention=linear_attention,
                          add_layernorm=add_layernorm, act_mul=act_mul, latent_prepare=latent_prepare, latent_rotate_q=latent_rotate_q,
                          latent_attention=latent_attention, headwise_linear=headwise_linear, route=route, group_pairs=group_pairs,
-                         expert_linear=expert_linear, combine_pairs=combine_pairs).items():
+                         expert_linear=expert_linear, combine_pairs=combine_pairs, head_gate=head_gate, bias_act=bias_act,
+                         add_row_vector=add_row_vector, gated_norm=gated_norm, scale_to_places=scale_to_places,
+                         token_shift_mix=token_shift_mix, wkv_scan=wkv_scan).items():
         monkeypatch.setattr(ops, name, fn)
     monkeypatch.setattr(ops, "device_error_flag", lambda device: flag)
     monkeypatch.setattr(ops, "check_device_errors", lambda device="cpu": None)
