@@ -698,7 +698,7 @@ def run_pivinex(args) -> dict:
                 "qkv": {"bytes": L * (down_cols * H * 2 + Tn * (H + down_cols) * 2), "flops": 2.0 * L * Tn * H * down_cols},
                 "q_up": {"bytes": L * (nh * (dn + dr) * qr * 2 + Tn * (qr + nh * (dn + dr)) * 2), "flops": 2.0 * L * Tn * qr * nh * (dn + dr)},
                 "absorb": {"bytes": L * (nh * dn * kr * 2 + Tn * nh * (dn + kr) * 2), "flops": 2.0 * L * Tn * nh * dn * kr},
-                "attention": {"bytes": L * (cached * row * 2 + Tn * nh * (row + kr) * 2), "flops": 2.0 * L * nh * (kr + dr + kr) * keys},
+                "latent_attention": {"bytes": L * (cached * row * 2 + Tn * nh * (row + kr) * 2), "flops": 2.0 * L * nh * (kr + dr + kr) * keys},
                 "v_up": {"bytes": L * (nh * dv * kr * 2 + Tn * nh * (kr + dv) * 2), "flops": 2.0 * L * Tn * nh * kr * dv},
                 "o": {"bytes": L * (H * nh * dv * 2 + Tn * (nh * dv + H) * 2), "flops": 2.0 * L * Tn * nh * dv * H},
                 "gate_up": {"bytes": 2 * I * H * 2 + Tn * (H + 2 * I) * 2 + Tn * 3 * I * 2, "flops": 4.0 * Tn * H * I},
@@ -773,6 +773,192 @@ def run_pivinex(args) -> dict:
             block["models"][name] = res
             del eng, st, cache
             torch.cuda.empty_cache()
+        out["sizes"][tag] = block
+    return out
+
+
+def _measure_design(cfg, work, args, peaks, V, T, ctx_len, rng, batches=(8, 64)) -> dict:
+    """One engine with random weights of ``cfg``: the device time of a ``T``-token prompt step (median of a few) and of
+    decode steps at the given batch sizes with ``ctx_len`` tokens of context, each with its per-class table;
+    ``work(tokens, entries, context_before)`` gives the classes' bytes and flops."""
+    import torch
+
+    from pyre_b200 import Engine
+    from pyre_b200.engine.step import StepEntry
+
+    biggest, reps = max(batches), max(3, args.prefill_reps)
+    eng = Engine(config=cfg, seed=0, dtype="bfloat16", device="cuda:0", page_size=PAGE_SIZE,
+                 max_cache_tokens=biggest * (ctx_len + 256) + 4 * T, max_num_seqs=biggest + 1, max_num_batched_tokens=T,
+                 prefill_chunk=T, max_model_len=ctx_len + 256)
+    st, cache = eng.stepper, eng.cache
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    def prompt(rid, n=T):
+        cache.begin(rid)
+        return st.step([StepEntry(rid, rng.integers(0, V, n).tolist(), [n - 1])])
+
+    for i in range(2):
+        prompt(("warm", i))
+        cache.end(("warm", i))
+    times = []
+    for i in range(reps):
+        a, b = ev(), ev()
+        a.record()
+        prompt(("pf", i))
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+        cache.end(("pf", i))
+    res = {"prefill_ms": round(sorted(times)[len(times) // 2], 3)}
+    res["prefill_tok_s"] = round(T / res["prefill_ms"] * 1e3, 1)
+    with st.kernel_timing() as timer:
+        prompt("timed")
+    cache.end("timed")
+    res["prefill_kernels"] = kernel_table(timer.totals(), work(T, 1, 0), res["prefill_ms"] * 1e3, peaks)
+    for i in range(biggest):
+        prompt(("d", i), ctx_len)
+    for B in batches:
+        reqs = [("d", i) for i in range(B)]
+        step = lambda: st.step([StepEntry(r, [int(rng.integers(0, V))], [0]) for r in reqs])
+        for _ in range(max(4, args.warmup)):
+            step()
+        torch.cuda.synchronize()
+        n = min(args.steps, 32)
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(n):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / n
+        res[f"decode_b{B}_ms"] = round(ms, 4)
+        res[f"decode_b{B}_tok_s"] = round(B / ms * 1e3, 1)
+        with st.kernel_timing() as timer:
+            step()
+        res[f"decode_b{B}_kernels"] = kernel_table(timer.totals(), work(B, B, ctx_len + 40), ms * 1e3, peaks)
+    del eng, st, cache
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_tekarax(args) -> dict:
+    """``--workload tekarax``: the Tekarax design (random weights) at two sets of layer sizes, three layers (a
+    recurrent one with a dense feed-forward, a windowed latent-attention one with routed experts, a softmax-attention
+    one with a dense feed-forward), beside the package's closest layers at equal sizes: Modovik's constant-decay
+    recurrent layer and its attention layer with dense feed-forwards, and Pivinex's latent-attention layer with routed
+    experts.  A 2,048-token prompt step and decode steps at batch 8 and 64 with 2,048 tokens of context, device-timed,
+    and per kernel class the device time of one such step with the fraction of the measured peak."""
+    import numpy as np
+
+    from pyre_b200.config import config_from_dict
+
+    peaks = load_peaks()
+    V = 32768
+    sizes = {
+        # width, attention heads / kv heads / dim, recurrent head size and decay map, latent rank and window, feed-forwards
+        "2k": dict(H=2048, nh=16, nkv=4, hd=128, wd=64, wr=64, kr=320, win=1024, I=8192, E=32, top=4, ff=1024, sh=2048),
+        "3.5k": dict(H=3584, nh=28, nkv=4, hd=128, wd=64, wr=96, kr=512, win=4096, I=18944, E=64, top=6, ff=1408, sh=2816),
+    }
+    T, ctx_len = PROMPT_LEN, 2048
+    rng = np.random.default_rng(0)
+    out = {"workload": "tekarax", "peaks": peaks, "prompt": T, "decode_context": ctx_len, "sizes": {}}
+    for tag, z in sizes.items():
+        H, nh, nkv, hd, wd, wr, kr, win, I, E, top, ff, sh = (z[k] for k in ("H", "nh", "nkv", "hd", "wd", "wr", "kr", "win", "I", "E", "top", "ff", "sh"))
+        wh = H // wd                                           # recurrent heads: heads x size = width
+        q, kv, row = nh * hd, nkv * hd, -(-kr // 16) * 16
+        rot = {"dims": 64, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+        moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top}, "shared": {"ff": sh}}
+        raw_t = {"architecture": "Tekarax", "vocab": V, "width": H, "norm": {"eps": 1e-6}, "layers": [
+            {"type": "wkv", "mixer": {"heads": wh, "dim": wd, "decay_rank": wr}, "mlp": {"kind": "dense", "ff": I}},
+            {"type": "latent_attention", "mixer": {"heads": nh, "dim": hd, "vdim": hd, "kv_rank": kr, "scale": hd ** -0.5, "mask": {"size": win}}, "mlp": moe},
+            {"type": "attention", "mixer": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "rot": rot},
+             "mlp": {"kind": "dense", "ff": I}}]}
+        raw_m = {"architecture": "Modovik", "vocab": V, "width": H, "norm": {"eps": 1e-6}, "layers": [
+            {"type": "lightning", "mixer": {"heads": wh, "dim": wd, "vdim": wd, "decay": [1.0 - 2.0 ** (-5 - 3 * i / wh) for i in range(wh)]},
+             "mlp": {"kind": "dense", "ff": I}},
+            {"type": "attention", "mixer": dict(heads=nh, kv_heads=nkv, dim=hd, vdim=hd, scale=hd ** -0.5, rot={"dims": 64, "base": 1e6}),
+             "mlp": {"kind": "dense", "ff": I}}]}
+        pr = min(64, kr // 4)                                  # Pivinex rotates a part of each row: rank + part = the same row size
+        raw_p = {"architecture": "Pivinex", "vocab": V, "width": H, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "layers": [
+            {"type": "latent_attention", "mixer": {"heads": nh, "dim": hd, "rot_dim": pr, "vdim": hd, "q_rank": 768, "kv_rank": kr - pr,
+                                                   "scale": (hd + pr) ** -0.5, "mask": {"size": win}, "rot": {"dims": pr, "base": 1e6}},
+             "mlp": {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "identity": 0, "top": top, "scale": 1.0}}}]}
+        whd = wh * wd
+
+        def attention_pairs(Tn, B, before, window=None):
+            first = np.arange(before, before + Tn // B)
+            return B * float((np.minimum(first + 1, window) if window else first + 1).sum())
+
+        def dense(Tn, n):
+            return {"up": {"bytes": n * (I * H * 2 + Tn * (H + I) * 2), "flops": 2.0 * n * Tn * H * I},
+                    "down": {"bytes": n * (H * I * 2 + Tn * (I + H) * 2), "flops": 2.0 * n * Tn * H * I}}
+
+        def routed(Tn, shared):
+            pairs = Tn * top
+            used = min(E, pairs)
+            return {"experts_gate_up": {"bytes": used * 2 * ff * H * 2 + pairs * (H + 2 * ff) * 2, "flops": 4.0 * pairs * H * ff},
+                    "experts_down": {"bytes": used * H * ff * 2 + pairs * (ff * 2 + H * 4), "flops": 2.0 * pairs * H * ff},
+                    "router": {"bytes": E * H * 4 + Tn * H * 2 + pairs * H * (4 + 2) + Tn * H * 4, "flops": 2.0 * Tn * H * E},
+                    **({"gate_up": {"bytes": 2 * shared * H * 2 + Tn * (H + 2 * shared) * 2, "flops": 4.0 * Tn * H * shared}} if shared else {})}
+
+        def tail(Tn, B):
+            return {"head": {"bytes": V * H * 2 + B * (H * 2 + V * 4), "flops": 2.0 * B * H * V}, "embed": {"bytes": Tn * H * (2 + 4), "flops": 0}}
+
+        def work_tekarax(Tn, B, before):
+            proj = 4 * whd + (q + 2 * kv + nh) + kr            # r k v g | q k v gates | latent
+            cached_l = B * min(before + Tn // B, win + Tn // B)
+            cached_a = B * (before + Tn // B)
+            w = {
+                "qkv": {"bytes": proj * H * 2 + Tn * (6 * H + proj) * 2, "flops": 2.0 * Tn * H * proj},
+                "decay": {"bytes": (wr * H + whd * wr) * 2 + Tn * (H + 2 * wr) * 2 + Tn * whd * 4, "flops": 2.0 * Tn * wr * (H + whd)},
+                "recurrence": {"bytes": Tn * (H * 2 * 6 + whd * (2 * 5 + 4)) + B * (2 * wh * wd * wd + 2 * H) * 4, "flops": 6.0 * Tn * wh * wd * wd},
+                "q_up": {"bytes": q * H * 2 + Tn * (H + q) * 2, "flops": 2.0 * Tn * H * q},
+                "absorb": {"bytes": nh * hd * kr * 2 + Tn * nh * (hd + row) * 2, "flops": 2.0 * Tn * nh * hd * kr},
+                "v_up": {"bytes": nh * hd * kr * 2 + Tn * nh * (kr + hd) * 2, "flops": 2.0 * Tn * nh * kr * hd},
+                "latent_attention": {"bytes": cached_l * row * 2 + Tn * nh * (row + kr) * 2, "flops": 4.0 * nh * kr * attention_pairs(Tn, B, before, win)},
+                "attention": {"bytes": cached_a * 2 * kv * 2 + 2 * Tn * q * 2, "flops": 4.0 * nh * hd * attention_pairs(Tn, B, before)},
+                "o": {"bytes": (whd + 2 * q) * H * 2 + Tn * (whd + 2 * q + 3 * H) * 2, "flops": 2.0 * Tn * H * (whd + 2 * q)},
+                "residual_gate": {"bytes": 6 * (H * H * 2 + Tn * 2 * H * 2), "flops": 2.0 * 6 * Tn * H * H},
+                "activation": {"bytes": 2 * Tn * I * 4 + Tn * top * 3 * ff * 2 + Tn * 3 * sh * 2 + Tn * wr * 4, "flops": 0},
+                "norm": {"bytes": Tn * H * (2 + 2 + 4 + 4), "flops": 0, "per_launch": True},
+                "gate": {"bytes": Tn * q * (2 + 2), "flops": 0, "per_launch": True},
+                "rotary+write": {"bytes": Tn * (q + 2 * kv) * 2 * 2, "flops": 0, "per_launch": True},
+                **dense(Tn, 2), **routed(Tn, sh), **tail(Tn, B)}
+            return w
+
+        def work_modovik(Tn, B, before):
+            proj = 4 * whd + (2 * q + 2 * kv)
+            return {
+                "qkv": {"bytes": proj * H * 2 + Tn * (2 * H + proj) * 2, "flops": 2.0 * Tn * H * proj},
+                "attention": {"bytes": B * (before + Tn // B) * 2 * kv * 2 + 2 * Tn * q * 2, "flops": 4.0 * nh * hd * attention_pairs(Tn, B, before)},
+                "linear_attention": {"bytes": Tn * 3 * whd * 2 + Tn * whd * 4 + B * 2 * wh * wd * wd * 4, "flops": 4.0 * Tn * wh * wd * wd},
+                "o": {"bytes": (whd + q) * H * 2 + Tn * (whd + q + 2 * H) * 2, "flops": 2.0 * Tn * H * (whd + q)},
+                "activation": {"bytes": 2 * Tn * I * 4, "flops": 0},
+                "norm": {"bytes": Tn * H * (2 + 4 + 4 + 2), "flops": 0, "per_launch": True},
+                "gate": {"bytes": Tn * q * (2 + 2 + 2), "flops": 0, "per_launch": True},
+                "rotary+write": {"bytes": Tn * (q + 2 * kv) * 2 * 2, "flops": 0, "per_launch": True},
+                **dense(Tn, 2), **tail(Tn, B)}
+
+        def work_pivinex(Tn, B, before):
+            down_cols = 768 + kr
+            cached = B * min(before + Tn // B, win + Tn // B)
+            return {
+                "qkv": {"bytes": down_cols * H * 2 + Tn * (H + down_cols) * 2, "flops": 2.0 * Tn * H * down_cols},
+                "q_up": {"bytes": nh * (hd + pr) * 768 * 2 + Tn * (768 + nh * (hd + pr)) * 2, "flops": 2.0 * Tn * 768 * nh * (hd + pr)},
+                "absorb": {"bytes": nh * hd * (kr - pr) * 2 + Tn * nh * (hd + kr) * 2, "flops": 2.0 * Tn * nh * hd * (kr - pr)},
+                "latent_attention": {"bytes": cached * row * 2 + Tn * nh * (row + kr) * 2, "flops": 2.0 * nh * (2 * kr - pr) * attention_pairs(Tn, B, before, win)},
+                "v_up": {"bytes": nh * hd * (kr - pr) * 2 + Tn * nh * (kr + hd) * 2, "flops": 2.0 * Tn * nh * (kr - pr) * hd},
+                "o": {"bytes": H * q * 2 + Tn * (q + H) * 2, "flops": 2.0 * Tn * q * H},
+                "activation": {"bytes": Tn * top * 3 * ff * 2, "flops": 0},
+                "norm": {"bytes": Tn * H * (2 + 2 + 4 + 4 + 2), "flops": 0, "per_launch": True},
+                "rotary+write": {"bytes": Tn * (down_cols + 768 + row) * 2, "flops": 0, "per_launch": True},
+                **routed(Tn, 0), **tail(Tn, B)}
+
+        block = {"sizes": dict(z, recurrent_heads=wh), "models": {}}
+        for name, raw, work in (("tekarax", raw_t, work_tekarax), ("modovik", raw_m, work_modovik), ("pivinex", raw_p, work_pivinex)):
+            block["models"][name] = dict(layers=len(raw["layers"]), **_measure_design(config_from_dict(raw), work, args, peaks, V, T, ctx_len, rng))
         out["sizes"][tag] = block
     return out
 
@@ -900,10 +1086,11 @@ def main() -> int:
                     help="leave out the points at longer contexts and at the 14B and 32B shapes")
     ap.add_argument("--no-per-kernel", action="store_true",
                     help="leave out the `kernels` block (device time, bytes or flops and fraction of the peak per kernel class)")
-    ap.add_argument("--workload", choices=["serve14b", "mixed32b", "sweep", "modovik", "pivinex"], default=None,
+    ap.add_argument("--workload", choices=["serve14b", "mixed32b", "sweep", "modovik", "pivinex", "tekarax"], default=None,
                     help="run one of the two other baseline workloads, a sweep over batch sizes, context lengths and "
-                         "portion lengths on the 7B shape, or the Modovik or the Pivinex design beside the Qwen2.5 decoder at "
-                         "equal layer sizes, instead (prints its own JSON line)")
+                         "portion lengths on the 7B shape, the Modovik or the Pivinex design beside the Qwen2.5 decoder at "
+                         "equal layer sizes, or the Tekarax design beside the closest layers of those two, instead (prints "
+                         "its own JSON line)")
     ap.add_argument("--cache-fraction", type=float, default=1.0,
                     help="serve14b: cache capacity as a fraction of what all requests need at once (< 1 forces preemption)")
     args = ap.parse_args()
@@ -912,7 +1099,7 @@ def main() -> int:
         return 2
     if args.workload:
         result = run_sweep(args) if args.workload == "sweep" else run_modovik(args) if args.workload == "modovik" else \
-            run_pivinex(args) if args.workload == "pivinex" else run_workload(args)
+            run_pivinex(args) if args.workload == "pivinex" else run_tekarax(args) if args.workload == "tekarax" else run_workload(args)
         result["env"] = environment()
         print(json.dumps(result))
         return 0

@@ -51,68 +51,113 @@ PYRE_API int pyre_token_shift_mix(const void* h, const float* state, long long s
 //   o_t[j] = sum_i r_t[i] (S[i][j] + u[i] k_t[i] v_t[j])        the current token counts with the bonus only
 //   S[i][j] = w_t[i] S[i][j] + k_t[i] v_t[j]
 //   out[t, h d + j] = T( o_t[j] / sqrt(mean_j(o_t^2) + eps) * norm_w[h d + j] * silu(g[t, h d + j]) )
-// One block per (head, entry); thread j keeps column j of S in registers and walks the entry's tokens in order,
-// so a token's result does not depend on how the request was cut into steps or on what else the step holds.
-// Block (0, b) also leaves the entry's last input row in the state slot for the next step's blend.
+// One CTA per (head, entry) holds the head's whole state in registers: a warp owns eight columns j, and its lanes
+// split the rows four ways in groups of four (row = 16 g + 4 q + e), so r, k and the decays come from shared
+// memory as conflict-free 16-byte loads and the four row groups of a column meet in two shuffles.  Tokens are
+// staged through shared memory sixteen at a time (decays evaluated while staging, all threads at once); the sixteen
+// tokens then run without a barrier, and their unit norm, gain and gate follow for all sixteen in parallel.  A
+// token's arithmetic is the same wherever its chunk begins, so a result does not depend on how the request was cut
+// into steps or on what else the step holds.  Block (0, b) also leaves the entry's last input row in the state
+// slot for the next step's blend.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ float wkv_silu(float z) { return z / (1.0f + expf(-z)); }
 
-template <typename T, int MAXD>
-__global__ void __launch_bounds__(MAXD) wkv_scan_kernel(const T* r, const T* k, const T* v, const T* g, const float* dlog,
-                                                        const float* w0, const float* u, const float* norm_w, float* state,
-                                                        long long slot_stride, long long prev_off, const int* slots,
-                                                        const int* cu_seqlens, const T* h, T* out, int H, int d, int W,
-                                                        float eps) {
-    __shared__ float sr[MAXD], sk[MAXD], sw[MAXD], su[MAXD];
-    __shared__ float scratch[33];
+constexpr int WKV_CHUNK = 16;      // tokens staged at a time
+
+// G: groups of 16 rows (d <= 16 G); a thread holds 4 G state elements of one column; ceil(d / 8) warps
+template <typename T, int G>
+__global__ void __launch_bounds__(G * 64) wkv_scan_kernel(const T* r, const T* k, const T* v, const T* g, const float* dlog,
+                                                          const float* w0, const float* u, const float* norm_w, float* state,
+                                                          long long slot_stride, long long prev_off, const int* slots,
+                                                          const int* cu_seqlens, const T* h, T* out, int H, int d, int W,
+                                                          float eps) {
+    constexpr int DP = 16 * G;
+    __shared__ __align__(16) float sr[WKV_CHUNK][DP];
+    __shared__ __align__(16) float sk[WKV_CHUNK][DP];
+    __shared__ __align__(16) float sw[WKV_CHUNK][DP];
+    __shared__ float sv[WKV_CHUNK][DP];
+    __shared__ float so[WKV_CHUNK][DP];
     pdl_trigger();
     pdl_wait();
-    const int head = blockIdx.x, b = blockIdx.y, j = threadIdx.x;
+    const int head = blockIdx.x, b = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int jj = lane & 7, q = lane >> 3;
+    const int col = warp * 8 + jj;
+    const bool col_ok = col < d;
     const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
     float* slot = state + (size_t)slots[b] * slot_stride;
     float* Sg = slot + (size_t)head * d * d;
-    const bool own = j < d;
-    const int col = head * d + j;
-    float S[MAXD];
-#pragma unroll
-    for (int i = 0; i < MAXD; ++i) S[i] = (own && i < d) ? Sg[(size_t)i * d + j] : 0.f;
-    if (own) su[j] = u[col];
-    const float nw = own ? norm_w[col] : 0.f;
-    const float wz = own ? w0[col] : 0.f;
     const size_t HD = (size_t)H * d;
-    for (int t = t0; t < t1; ++t) {
-        __syncthreads();      // the token before is done with sr / sk / sw
-        float vj = 0.f;
-        if (own) {
-            sr[j] = to_f32<T>(r[t * HD + col]);
-            sk[j] = to_f32<T>(k[t * HD + col]);
-            sw[j] = expf(-expf(dlog[t * HD + col] + wz));
-            vj = to_f32<T>(v[t * HD + col]);
+    const size_t base = (size_t)head * d;
+
+    float S[4 * G], ub[4 * G];
+#pragma unroll
+    for (int gg = 0; gg < G; ++gg)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int i = 16 * gg + 4 * q + e;
+            S[4 * gg + e] = (col_ok && i < d) ? Sg[(size_t)i * d + col] : 0.f;
+            ub[4 * gg + e] = i < d ? u[base + i] : 0.f;
+        }
+
+    for (int c0 = t0; c0 < t1; c0 += WKV_CHUNK) {
+        const int n = min(WKV_CHUNK, t1 - c0);
+        __syncthreads();      // the chunk before is done with the staged rows and its outputs
+        for (int e = threadIdx.x; e < n * DP; e += blockDim.x) {
+            const int tt = e / DP, i = e - tt * DP;
+            const size_t at = (size_t)(c0 + tt) * HD + base + i;
+            const bool real = i < d;
+            sr[tt][i] = real ? to_f32<T>(r[at]) : 0.f;
+            sk[tt][i] = real ? to_f32<T>(k[at]) : 0.f;
+            sv[tt][i] = real ? to_f32<T>(v[at]) : 0.f;
+            sw[tt][i] = real ? expf(-expf(dlog[at] + w0[base + i])) : 0.f;
         }
         __syncthreads();
-        float o = 0.f;
+        for (int tt = 0; tt < n; ++tt) {
+            const float vj = sv[tt][col];
+            float acc = 0.f;
 #pragma unroll
-        for (int i = 0; i < MAXD; ++i) {
-            if (i < d) {
-                const float kv = sk[i] * vj;
-                o = fmaf(sr[i], fmaf(su[i], kv, S[i]), o);
-                S[i] = fmaf(sw[i], S[i], kv);
+            for (int gg = 0; gg < G; ++gg) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&sk[tt][16 * gg + 4 * q]);
+                const float4 r4 = *reinterpret_cast<const float4*>(&sr[tt][16 * gg + 4 * q]);
+                const float4 w4 = *reinterpret_cast<const float4*>(&sw[tt][16 * gg + 4 * q]);
+                const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, rr[4] = {r4.x, r4.y, r4.z, r4.w}, ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float kv = kk[e] * vj;
+                    acc = fmaf(rr[e], fmaf(ub[4 * gg + e], kv, S[4 * gg + e]), acc);
+                    S[4 * gg + e] = fmaf(ww[e], S[4 * gg + e], kv);
+                }
             }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+            if (q == 0) so[tt][col] = acc;
         }
-        const float ss = block_sum(own ? o * o : 0.f, scratch);
-        if (own) {
+        __syncthreads();
+        // the chunk's tokens, one warp each: unit norm over the head, gain, gate
+        for (int tt = warp; tt < n; tt += n_warps) {
+            float ss = 0.f;
+            for (int j = lane; j < d; j += 32) ss = fmaf(so[tt][j], so[tt][j], ss);
+#pragma unroll
+            for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
             const float rstd = 1.0f / sqrtf(ss / (float)d + eps);
-            out[t * HD + col] = from_f32<T>(__fmul_rn(__fmul_rn(o, rstd), nw) * wkv_silu(to_f32<T>(g[t * HD + col])));
+            const size_t at = (size_t)(c0 + tt) * HD + base;
+            for (int j = lane; j < d; j += 32)
+                out[at + j] = from_f32<T>(__fmul_rn(__fmul_rn(so[tt][j], rstd), norm_w[base + j]) * wkv_silu(to_f32<T>(g[at + j])));
         }
     }
-    if (own) {
+    if (col_ok) {
 #pragma unroll
-        for (int i = 0; i < MAXD; ++i)
-            if (i < d) Sg[(size_t)i * d + j] = S[i];
+        for (int gg = 0; gg < G; ++gg)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = 16 * gg + 4 * q + e;
+                if (i < d) Sg[(size_t)i * d + col] = S[4 * gg + e];
+            }
     }
     if (head == 0 && t1 > t0) {
         const T* last = h + (size_t)(t1 - 1) * W;
-        for (int i = j; i < W; i += MAXD) slot[prev_off + i] = to_f32<T>(last[i]);
+        for (int i = threadIdx.x; i < W; i += blockDim.x) slot[prev_off + i] = to_f32<T>(last[i]);
     }
 }
 
@@ -125,8 +170,10 @@ PYRE_API int pyre_wkv_scan(const void* r, const void* k, const void* v, const vo
         return PYRE_ERR_BAD_ARG;
     if (d > 128) return PYRE_ERR_UNSUPPORTED;
     const dim3 grid(H, n_seqs);
-#define WKV(TT, MD) pyre_launch(wkv_scan_kernel<TT, MD>, grid, dim3(MD), 0, stream, (const TT*)r, (const TT*)k, (const TT*)v, (const TT*)g, dlog, w0, u, norm_w, state, slot_stride, prev_off, slots, cu_seqlens, (const TT*)h, (TT*)out, H, d, W, eps)
-#define WKV_PICK(TT) do { if (d <= 32) WKV(TT, 32); else if (d <= 64) WKV(TT, 64); else WKV(TT, 128); } while (0)
+    const dim3 block(((d + 7) / 8) * 32);
+#define WKV(TT, GG) pyre_launch(wkv_scan_kernel<TT, GG>, grid, block, 0, stream, (const TT*)r, (const TT*)k, (const TT*)v, (const TT*)g, dlog, w0, u, norm_w, state, slot_stride, prev_off, slots, cu_seqlens, (const TT*)h, (TT*)out, H, d, W, eps)
+#define WKV_PICK(TT) do { if (d <= 16) WKV(TT, 1); else if (d <= 32) WKV(TT, 2); else if (d <= 48) WKV(TT, 3); else if (d <= 64) WKV(TT, 4); \
+                          else if (d <= 96) WKV(TT, 6); else WKV(TT, 8); } while (0)
     if (dtype == PYRE_BF16) WKV_PICK(__nv_bfloat16);
     else if (dtype == PYRE_F32) WKV_PICK(float);
     else return PYRE_ERR_BAD_ARG;

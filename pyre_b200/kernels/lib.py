@@ -92,7 +92,7 @@ DEFAULT_CLASS = {
     "pyre_sigmoid_gate": "gate", "pyre_rmsnorm_gate": "gate", "pyre_linear_attention_scan": "linear_attention",
     "pyre_linear_attention_chunked": "linear_attention",
     "pyre_add_layernorm": "norm", "pyre_scaled_sum": "norm", "pyre_act_mul": "activation", "pyre_latent_prepare": "rotary+write",
-    "pyre_latent_rotate_q": "rotary+write", "pyre_latent_attention_exact": "attention", "pyre_latent_attention_mma": "attention", "pyre_grouped_linear": "grouped_product",
+    "pyre_latent_rotate_q": "rotary+write", "pyre_latent_attention_exact": "latent_attention", "pyre_latent_attention_mma": "latent_attention", "pyre_grouped_linear": "grouped_product",
     "pyre_route": "router", "pyre_group_pairs": "router", "pyre_combine_pairs": "router", "pyre_scale_to_places": "router",
     "pyre_head_gate": "gate", "pyre_bias_act": "activation", "pyre_add_row_vector": "norm", "pyre_gated_norm": "norm",
     "pyre_token_shift_mix": "recurrence", "pyre_wkv_scan": "recurrence",

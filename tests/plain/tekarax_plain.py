@@ -75,6 +75,18 @@ def rotate_halves(v, positions, freqs, sign=1.0):
     return torch.cat([a * c - b * s, b * c + a * s, v[..., 2 * n:]], dim=-1)
 
 
+def softmax_with_sink(scores, sink=None):
+    """Softmax over the last axis whose denominator holds one more term, exp(sink): a sink has a score (as it is, not
+    scaled) and no value, so the weights of a row sum to less than one."""
+    m = scores.max(-1, keepdim=True).values
+    if sink is None:
+        e = torch.exp(scores - m)
+        return e / e.sum(-1, keepdim=True)
+    m = torch.maximum(m, torch.as_tensor(sink, dtype=scores.dtype).expand_as(m))
+    e = torch.exp(scores - m)
+    return e / (e.sum(-1, keepdim=True) + torch.exp(sink - m))
+
+
 def attention(h, w, prefix, mixer, lowp=False):
     """Grouped-query softmax attention, causal, with rotated queries and keys (leading dims, scaled frequencies),
     values rotated by their own position over all their dims and each head's sum turned back by the query's position,
@@ -101,12 +113,7 @@ def attention(h, w, prefix, mixer, lowp=False):
         kv = n // (H // G)
         s = (q[:, n] @ k[:, kv].T) * mixer["scale"]
         s = s.masked_fill(~causal, -math.inf)
-        m = s.max(-1, keepdim=True).values
-        if sink is not None:
-            m = torch.maximum(m, sink[n].expand_as(m))
-        e = torch.exp(s - m)
-        den = e.sum(-1, keepdim=True) + (torch.exp(sink[n] - m) if sink is not None else 0.0)
-        out[:, n] = (e / den) @ v[:, kv]
+        out[:, n] = softmax_with_sink(s, sink[n] if sink is not None else None) @ v[:, kv]
     if rot:
         out = rotate_halves(out, pos, fv, sign=-1.0)
     if prefix + "g" in w:
@@ -138,6 +145,26 @@ def latent_attention(h, w, prefix, mixer, eps, lowp=False):
     return matmul(_r(out, lowp).reshape(T, H * dv), g("o"), lowp)
 
 
+def token_blend(h, mu, before=None):
+    """h_t + (h_(t-1) - h_t) * mu; the row before the first is ``before`` (zeros when a sequence begins)."""
+    first = torch.zeros(1, h.shape[1], dtype=h.dtype) if before is None else before.reshape(1, -1)
+    prev = torch.cat([first, h[:-1]], dim=0)
+    return h + (prev - h) * mu
+
+
+def wkv_recurrence(r, k, v, decay, u, S=None):
+    """Per head n: o_t = (S + diag(u) k_t v_t^T)^T r_t, then S = diag(decay_t) S + k_t v_t^T.  r, k, v, decay
+    [T, H, d]; u [H, d]; S [H, d, d] (zeros when a sequence begins).  Returns (o [T, H, d], the state after)."""
+    T, H, d = r.shape
+    S = torch.zeros(H, d, d, dtype=r.dtype) if S is None else S.clone()
+    out = torch.zeros(T, H, d, dtype=r.dtype)
+    for t in range(T):
+        kv = k[t][:, :, None] * v[t][:, None, :]
+        out[t] = torch.einsum("hi,hij->hj", r[t], S + u[:, :, None] * kv)
+        S = decay[t][:, :, None] * S + kv
+    return out, S
+
+
 def wkv(h, w, prefix, mixer, eps, lowp=False):
     """Time mixing with a matrix state per head: each of r, k, v, g, w reads its own blend of the token's input and
     the previous token's; a decay per head and key channel from a small two-layer map; the current token's key-value
@@ -145,8 +172,7 @@ def wkv(h, w, prefix, mixer, eps, lowp=False):
     T, width = h.shape
     H, d = mixer["heads"], mixer["dim"]
     g = lambda n: w[prefix + n].to(F64)
-    prev = torch.cat([torch.zeros(1, width, dtype=F64), h[:-1]], dim=0)
-    mix = lambda s: _r(h + (prev - h) * g("mu." + s), lowp)
+    mix = lambda s: _r(token_blend(h, g("mu." + s)), lowp)
     r = matmul(mix("r"), g("r"), lowp).view(T, H, d)
     k = matmul(mix("k"), g("k"), lowp).view(T, H, d)
     v = matmul(mix("v"), g("v"), lowp).view(T, H, d)
@@ -154,12 +180,7 @@ def wkv(h, w, prefix, mixer, eps, lowp=False):
     inner = _r(torch.tanh(matmul(mix("w"), g("w1"), lowp)), lowp)
     decay = torch.exp(-torch.exp(_r(inner, lowp) @ g("w2").T + g("w0"))).view(T, H, d)
     u = g("u").view(H, d)
-    S = torch.zeros(H, d, d, dtype=F64)
-    out = torch.zeros(T, H, d, dtype=F64)
-    for t in range(T):
-        kv = k[t][:, :, None] * v[t][:, None, :]
-        out[t] = torch.einsum("hi,hij->hj", r[t], S + u[:, :, None] * kv)
-        S = decay[t][:, :, None] * S + kv
+    out, _ = wkv_recurrence(r, k, v, decay, u)
     out = unit_rms(out, eps).reshape(T, H * d) * g("norm") * gate
     return matmul(_r(out, lowp), g("o"), lowp)
 
