@@ -86,6 +86,7 @@ TEK_D = {"architecture": "Tekarax", "vocab": 256, "width": 128, "norm": {"eps": 
 ]}
 TEK = {"A": TEK_A, "B": TEK_B, "C": TEK_C, "D": TEK_D}
 TEK_PAGE_SIZE = {"A": 16, "B": 8, "C": 32, "D": 16}
+NEIGHBOURS = 8
 ROUTER_MARGIN = 2e-2     # a router decision closer than this could fall either way under bfloat16 rounding of the stream
 
 
@@ -157,7 +158,8 @@ def compare(got: dict, want: dict, dtype: str, what: str, lowp_rms: float = 0.0,
     layer runs).  bfloat16: the engine's rms error against the plain implementation is at most twice that of the plain
     implementation rounded to bfloat16 where the engine may round (``lowp``, its logits per request), and no logit is
     off by more than sixteen times that rms plus three times the rounded plain implementation's own largest error at
-    that position: where a sublayer's result is small (the first tokens of a recurrent layer, whose state is still
+    that position or one of its eight neighbours on either side (what rounding does at one position is a matter of
+    chance; its neighbours show what it can do in that part of the sequence): where a sublayer's result is small (the first tokens of a recurrent layer, whose state is still
     nearly empty) the norm after it enlarges every rounding, for both alike, while a wrong key, page, slot or
     position moves logits by their whole spread at positions of every kind."""
     assert set(got) == set(want), f"{what}: requests differ"
@@ -170,7 +172,10 @@ def compare(got: dict, want: dict, dtype: str, what: str, lowp_rms: float = 0.0,
         if dtype == "float32":
             bound = 1e-4 + 2e-4 * np.abs(w)
         else:
-            own = np.abs(lowp[rid] - w).max(axis=1, keepdims=True) if lowp is not None else 0.0
+            own = 0.0
+            if lowp is not None:
+                rows = np.abs(lowp[rid] - w).max(axis=1)
+                own = np.array([rows[max(0, i - NEIGHBOURS):i + NEIGHBOURS + 1].max() for i in range(len(rows))])[:, None]
             bound = np.broadcast_to(16.0 * lowp_rms + 3.0 * own, w.shape)
         sq, cnt = sq + float((err.astype(np.float64) ** 2).sum()), cnt + err.size
         bad = err > bound
