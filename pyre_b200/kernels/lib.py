@@ -54,7 +54,7 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_add_row_vector": ("blockops", [P, P, LL, I, P]),
     "pyre_gated_norm": ("blockops", [P, P, I, LL, P, P, P, P, P, I, I, F, I, I, P]),
     "pyre_token_shift_mix": ("wkv", [P, P, LL, LL, P, P, P, P, P, I, I, I, I, P]),
-    "pyre_wkv_scan": ("wkv", [P, P, P, P, P, P, P, P, P, LL, LL, P, P, P, P, I, I, I, I, I, F, I, P]),
+    "pyre_wkv_scan": ("wkv", [P, P, P, P, P, P, P, P, P, LL, LL, P, P, P, P, P, I, I, I, I, I, F, I, P]),
     "pyre_linear_attention_scan": ("linear_attention", [P, LL, I, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P]),
     "pyre_linear_attention_chunked": ("linear_attention", [P, LL, I, I, I, P, P, P, P, P, I, I, I, I, I, I, I, P]),
     "pyre_add_layernorm": ("parallel_block", [P, P, P, I, P, P, P, I, P, LL, P, P, I, P, I, I, F, I, I, P]),

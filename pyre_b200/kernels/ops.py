@@ -1793,9 +1793,10 @@ def wkv_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor,
     if prev_off < n_heads * dim * dim or prev_off + W > state_layer.shape[1]:
         raise ValueError("the state slot does not hold the matrices and the input row")
     out = torch.empty((T, HD), dtype=r.dtype, device=r.device)
+    raw = torch.empty((T, HD), dtype=torch.float32, device=r.device)      # o before the unit norm, between the two kernels
     lib.call("pyre_wkv_scan", r.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), dlog.data_ptr(), w0.data_ptr(), u.data_ptr(),
              norm_w.data_ptr(), state_layer.data_ptr(), state_layer.shape[1], int(prev_off), slots.data_ptr(), cu_seqlens.data_ptr(),
-             h.data_ptr(), out.data_ptr(), T, n_seqs, n_heads, dim, W, float(eps), _dt(r.dtype), _stream())
+             h.data_ptr(), raw.data_ptr(), out.data_ptr(), T, n_seqs, n_heads, dim, W, float(eps), _dt(r.dtype), _stream())
     return out
 
 
