@@ -16,10 +16,10 @@ import time
 from pathlib import Path
 
 
-SIZES = ("Architectures: Qwen2ForCausalLM, Modovik and Pivinex (config.json names one).  "
+SIZES = ("Architectures: Qwen2ForCausalLM, Modovik, Pivinex and Tekarax (config.json names one).  "
          "Sizes: a head size must be a multiple of 16 up to 256 (others are refused when the model is built; Modovik's heads "
          "may have any size up to 256, their cache rows are padded; Pivinex caches one latent row per token, any size up to "
-         "512, padded to a multiple of 16).  "
+         "512, padded to a multiple of 16; Tekarax's recurrent heads may have any size up to 128).  "
          "In bfloat16, head sizes up to 128 run on the tensor-core attention kernels, larger ones on the exact "
          "fp32-arithmetic kernel, as every float32 run does (slower).  A bfloat16 product whose inner size is no "
          "multiple of 8 (a hidden or feed-forward size like 92) goes to a library product; every other product and "

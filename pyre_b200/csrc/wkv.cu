@@ -114,10 +114,10 @@ __device__ __forceinline__ void wkv_tokens(float (&S)[4 * G], const float (&ub)[
 
 template <typename T, int G>
 __global__ void __launch_bounds__(WkvShape<G>::THREADS)
-wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __restrict__ v, const float* __restrict__ dlog,
-                const float* __restrict__ w0, const float* __restrict__ u, float* state, long long slot_stride,
-                long long prev_off, const int* __restrict__ slots, const int* __restrict__ cu_seqlens,
-                const T* __restrict__ h, float* __restrict__ o_raw, int H, int d, int W) {
+wkv_scan_kernel(const T* r, const T* k, const T* v, const float* dlog,
+                const float* w0, const float* u, float* state, long long slot_stride,
+                long long prev_off, const int* slots, const int* cu_seqlens,
+                const T* h, float* o_raw, int H, int d, int W) {
     using Sh = WkvShape<G>;
     constexpr int DP = Sh::DP, THREADS = Sh::THREADS, CT = Sh::CT, PER = Sh::PER, PERV = Sh::PERV;
     __shared__ __align__(16) float sr[WKV_CHUNK][DP];
@@ -216,8 +216,8 @@ wkv_scan_kernel(const T* __restrict__ r, const T* __restrict__ k, const T* __res
 // out[t, h d + j] = T( o[j] / sqrt(mean_j(o^2) + eps) * norm_w[h d + j] * silu(g[t, h d + j]) ), o the raw result of
 // head h at token t: one warp per (token, head).
 template <typename T>
-__global__ void __launch_bounds__(128) wkv_finish_kernel(const float* __restrict__ o_raw, const T* __restrict__ g,
-                                                         const float* __restrict__ norm_w, T* __restrict__ out,
+__global__ void __launch_bounds__(128) wkv_finish_kernel(const float* o_raw, const T* g,
+                                                         const float* norm_w, T* out,
                                                          long long n_rows, int H, int d, float eps) {
     pdl_trigger();
     pdl_wait();

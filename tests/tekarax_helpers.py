@@ -67,12 +67,12 @@ TEK_B = {"architecture": "Tekarax", "vocab": 333, "width": 92, "norm": {"eps": 3
     _with(_latent(5, 20, 12, 36, 0.2, 7), _moe(28, 4, 1, 20)),
     _with(_wkv(5, 28, 12)),
 ]}
-# C: sizes of the tensor-core paths: heads of 64 over two key/value heads, a latent of 192, recurrent heads of 64, a
+# C: sizes of the tensor-core paths: heads of 64 over four key/value heads, a latent of 192, recurrent heads of 64, a
 #    window of 64 on pages of 32, the first two layers twice, feed-forwards wide enough for the fused products.
 TEK_C = {"architecture": "Tekarax", "vocab": 640, "width": 256, "norm": {"eps": 1e-6},
          "loop": {"start": 0, "stop": 2, "times": 2}, "layers": [
     _with(_latent(8, 64, 64, 192, 0.12, 64), _moe(128, 8, 2, 256)),
-    _with(_attn(8, 2, 64, 64, 0.12, 64, 1000000.0, (4.0, 1.0, 4.0, 256)), _dense(512)),
+    _with(_attn(8, 4, 64, 64, 0.12, 64, 500000.0, (3.0, 1.0, 4.0, 256)), _dense(512)),
     _with(_wkv(4, 64, 32), _dense(512)),
 ]}
 # D: one key/value head under six query heads of 128 with values of 64 and a rotation of a quarter of the head; one

@@ -404,7 +404,7 @@ def check_mixer(tmp_path, layer, width, eps, dtype, page, plain, seed):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,kv,dk,dv,rot,page,width", [(4, 2, 16, 24, 8, 16, 96), (5, 5, 20, 12, 12, 8, 92), (8, 2, 64, 64, 64, 32, 256),
+@pytest.mark.parametrize("heads,kv,dk,dv,rot,page,width", [(4, 2, 16, 24, 8, 16, 96), (5, 5, 20, 12, 12, 8, 92), (8, 4, 64, 64, 64, 32, 256),
                                                             (6, 1, 128, 64, 32, 16, 128), (2, 2, 32, 32, 0, 16, 64)])
 def test_attention_mixer_alone(tmp_path, dtype, heads, kv, dk, dv, rot, page, width):
     layer = TH._attn(heads, kv, dk, dv, 0.8 / math.sqrt(dk), rot, 100.0, (8.0, 1.0, 4.0, 32))
@@ -415,7 +415,7 @@ def test_attention_mixer_alone(tmp_path, dtype, heads, kv, dk, dv, rot, page, wi
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,dk,dv,rank,window,page,width", [(3, 16, 24, 24, 11, 16, 96), (5, 20, 12, 36, 7, 8, 92), (8, 64, 64, 192, 64, 32, 256),
-                                                                 (2, 48, 40, 64, 0, 16, 128), (4, 32, 32, 64, 1, 16, 64), (6, 32, 32, 64, 40, 16, 192)])
+                                                                 (2, 48, 40, 64, 0, 16, 128), (4, 32, 32, 64, 1, 16, 64), (6, 32, 24, 80, 37, 16, 160)])
 def test_latent_mixer_alone(tmp_path, dtype, heads, dk, dv, rank, window, page, width):
     """Windows of 1 (a token sees itself only), smaller and larger than a page, and none at all."""
     layer = TH._latent(heads, dk, dv, rank, 0.8 / math.sqrt(dk), window)
@@ -423,7 +423,7 @@ def test_latent_mixer_alone(tmp_path, dtype, heads, dk, dv, rank, window, page, 
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads,d,rank,width", [(3, 16, 8, 96), (4, 20, 12, 92), (4, 64, 32, 256), (1, 128, 24, 128), (4, 32, 16, 192)])
+@pytest.mark.parametrize("heads,d,rank,width", [(3, 16, 8, 96), (4, 20, 12, 92), (4, 64, 32, 256), (1, 128, 24, 128), (6, 32, 16, 160)])
 def test_wkv_mixer_alone(tmp_path, dtype, heads, d, rank, width):
     layer = TH._wkv(heads, d, rank)
     check_mixer(tmp_path, layer, width, 1e-5, dtype, 16, lambda h, w: TP.wkv(h, w, "l0.mix.", layer["mixer"], 1e-5), seed=heads)
