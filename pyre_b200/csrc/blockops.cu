@@ -555,22 +555,19 @@ __global__ void head_gate_kernel(const T* a, int a_dim, const T* proj, long long
                                  const float* sin_t, T* out, int n_tokens, int nh, int dv) {
     pdl_trigger();
     pdl_wait();
-    const int vh = dv / 2, row = nh * dv;
-    // blocks (x: tokens in turn, y: shares of a token's row, for steps of few tokens): 32-bit index arithmetic
-    for (int t = blockIdx.x; t < n_tokens; t += gridDim.x) {
-        for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < row; c += gridDim.y * blockDim.x) {
-            const int h = c / dv, j = c - h * dv;
-            const T* head = a + ((size_t)t * nh + h) * a_dim;
-            float u = to_f32<T>(head[j]);
-            if (cos_t) {
-                const float* ct = cos_t + (size_t)t * vh;
-                const float* st = sin_t + (size_t)t * vh;
-                if (j < vh) u = __fadd_rn(__fmul_rn(u, ct[j]), __fmul_rn(to_f32<T>(head[j + vh]), st[j]));
-                else if (j < 2 * vh) u = __fadd_rn(__fmul_rn(u, ct[j - vh]), __fmul_rn(-to_f32<T>(head[j - vh]), st[j - vh]));
-            }
-            const float gt = g_col >= 0 ? act_sigmoid(to_f32<T>(proj[(size_t)t * row_stride + g_col + h])) : 1.0f;
-            out[(size_t)t * row + c] = from_f32<T>(u * gt);
+    const int vh = dv / 2;
+    const size_t n = (size_t)n_tokens * nh * dv, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const size_t t = i / ((size_t)nh * dv);
+        const int c = (int)(i - t * nh * dv), h = c / dv, j = c - h * dv;
+        const T* head = a + (t * nh + h) * a_dim;
+        float u = to_f32<T>(head[j]);
+        if (cos_t) {
+            if (j < vh) u = __fadd_rn(__fmul_rn(u, cos_t[t * vh + j]), __fmul_rn(to_f32<T>(head[j + vh]), sin_t[t * vh + j]));
+            else if (j < 2 * vh) u = __fadd_rn(__fmul_rn(u, cos_t[t * vh + j - vh]), __fmul_rn(-to_f32<T>(head[j - vh]), sin_t[t * vh + j - vh]));
         }
+        const float gt = g_col >= 0 ? act_sigmoid(to_f32<T>(proj[t * row_stride + g_col + h])) : 1.0f;
+        out[i] = from_f32<T>(u * gt);
     }
 }
 
@@ -579,12 +576,12 @@ PYRE_API int pyre_head_gate(const void* a, int a_dim, const void* proj, long lon
     if (n_tokens <= 0) return 0;
     if (a_dim < dv || dv <= 0 || nh <= 0 || (g_col >= 0 && !proj) || (cos_t == nullptr) != (sin_t == nullptr) || (cos_t && dv % 2))
         return PYRE_ERR_BAD_ARG;
-    const int shares = max(1, min((nh * dv + 255) / 256, (148 * 4) / n_tokens));
-    const dim3 blocks(min(148 * 16, n_tokens), shares);
+    const long long n = (long long)n_tokens * nh * dv;
+    const int blocks = (int)min((long long)148 * 16, ceil_div_ll(n, 256));
     if (dtype == PYRE_BF16)
-        pyre_launch(head_gate_kernel<__nv_bfloat16>, blocks, dim3(256), 0, stream, (const __nv_bfloat16*)a, a_dim, (const __nv_bfloat16*)proj, row_stride, g_col, cos_t, sin_t, (__nv_bfloat16*)out, n_tokens, nh, dv);
+        pyre_launch(head_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)a, a_dim, (const __nv_bfloat16*)proj, row_stride, g_col, cos_t, sin_t, (__nv_bfloat16*)out, n_tokens, nh, dv);
     else if (dtype == PYRE_F32)
-        pyre_launch(head_gate_kernel<float>, blocks, dim3(256), 0, stream, (const float*)a, a_dim, (const float*)proj, row_stride, g_col, cos_t, sin_t, (float*)out, n_tokens, nh, dv);
+        pyre_launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)a, a_dim, (const float*)proj, row_stride, g_col, cos_t, sin_t, (float*)out, n_tokens, nh, dv);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;
