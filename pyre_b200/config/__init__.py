@@ -1,10 +1,10 @@
 from .engine_config import EngineConfig, parse_dtype
-from .model_config import ConfigError, ModelConfig, ModovikConfig, ModovikLayer, Qwen2Config, TekaraxConfig, TekaraxLayer
+from .model_config import ConfigError, ModelConfig, ModovikConfig, ModovikLayer, NipudraConfig, NipudraLayer, Qwen2Config, TekaraxConfig, TekaraxLayer
 from .registry import (Architecture, architecture, architecture_of, config_from_dict, load_config,
                        register_architecture, registered_architectures)
 
 __all__ = [
-    "Architecture", "ConfigError", "EngineConfig", "ModelConfig", "ModovikConfig", "ModovikLayer", "Qwen2Config", "TekaraxConfig", "TekaraxLayer", "architecture",
+    "Architecture", "ConfigError", "EngineConfig", "ModelConfig", "ModovikConfig", "ModovikLayer", "NipudraConfig", "NipudraLayer", "Qwen2Config", "TekaraxConfig", "TekaraxLayer", "architecture",
     "architecture_of", "config_from_dict", "load_config", "parse_dtype", "register_architecture",
     "registered_architectures",
 ]

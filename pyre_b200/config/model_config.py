@@ -603,3 +603,212 @@ class TekaraxConfig(ModelConfig):
                 L = dataclasses.replace(L, decay_rank=int(shape[0]))
             layers.append(L)
         return dataclasses.replace(self, layers=tuple(layers))
+
+
+@dataclass(frozen=True)
+class NipudraLayer:
+    """One layer of a Nipudra model: which mixer (``kind``: "attention", "mamba2" or "retention") with its sizes, and
+    its feed-forward: ``mlp_kind`` "moe" (``experts`` experts of ``ff``, ``top`` per token, plus a shared one of
+    ``shared_ff`` when that is positive) or "" (none)."""
+
+    kind: str
+    heads: int
+    vdim: int                      # value entries per head (mamba2: entries of x per head)
+    dim: int = 0                   # query/key entries per head and map (attention, retention)
+    kv_heads: int = 0              # attention: key/value heads
+    scale: float = 0.0             # attention: factor on q . k
+    diff: float = 0.0              # attention: the constant of lambda and of the heads' final factor 1 - diff
+    window: int = 0                # attention: a position sees itself and window - 1 before it (0: all)
+    kv_from: int = -1              # attention: the layer whose cached keys and values this one reads (-1: its own)
+    conv: int = 0                  # attention, mamba2: taps of the short convolution (attention: 0 = none)
+    rot_dims: int = 0              # attention, retention: leading entries of a head that are rotated
+    rot_base: float = 10000.0
+    rot_scaling: "tuple | None" = None      # attention: (factor, original, fast, slow) or None
+    decay: tuple = ()              # retention: one decay per head
+    state: int = 0                 # mamba2: rows of a head's state
+    groups: int = 0                # mamba2: groups that share B and C
+    norm_groups: int = 0           # mamba2: equal parts of the gated row, each with its own unit norm
+    mlp_kind: str = ""
+    ff: int = 0
+    experts: int = 0
+    top: int = 0
+    shared_ff: int = 0
+
+
+@dataclass(frozen=True)
+class NipudraConfig(ModelConfig):
+    """A Nipudra decoder: a scaled embedding; layers with a layer norm (gain and bias) before AND after each sublayer,
+    x += norm_b(sublayer(norm(x))); three kinds of mixer in any order (differential softmax attention over a sliding
+    window with short convolutions on q, k and v; a selective state-space recurrence; retention with a constant decay
+    per head); a routed feed-forward or none; a per-layer input from the token's row of a side table; a final layer
+    norm and a head tied to the embedding whose logits are scaled and soft-capped.  ``config.json`` keys: ``vocab``,
+    ``width``, ``norm.eps``, ``embedding.scale``, ``logit_scale``, ``logit_softcap``, ``token_side.dim`` and ``layers``,
+    a list of ``{"type", "mixer": {...}, "mlp": {"kind": "moe", "expert": {"ff"}, "router": {experts, top}, "shared":
+    {"ff"}} | null}`` with the mixers ``attention {heads, kv_heads, dim, vdim, scale, diff, conv, mask: {size}, kv_from,
+    rot: {dims, base, scaling: {factor, original, fast, slow}}}``, ``mamba2 {heads, vdim, state, groups, conv,
+    norm_groups}`` and ``retention {heads, dim, vdim, decay: [...], rot: {dims, base}}``.  The taps of a convolution
+    that the file leaves out are read from the shape of the layer's tensor (``with_tensor_shapes``)."""
+
+    architecture: ClassVar[str] = "Nipudra"
+    KINDS: ClassVar[tuple] = ("attention", "mamba2", "retention")
+
+    vocab: int
+    width: int
+    norm_eps: float
+    layers: tuple
+    embedding_scale: float = 1.0
+    logit_scale: float = 1.0
+    logit_softcap: float = 0.0
+    side_dim: int = 0
+
+    def __post_init__(self):
+        _positive("vocab", self.vocab)
+        _positive("width", self.width)
+        if not self.norm_eps > 0:
+            raise ConfigError(f"config.json: norm.eps must be positive, got {self.norm_eps}")
+        if not self.layers:
+            raise ConfigError("config.json: layers is empty")
+        if self.side_dim < 0 or self.logit_softcap < 0 or not self.logit_scale > 0:
+            raise ConfigError("config.json: token_side.dim and logit_softcap must not be negative, logit_scale positive")
+        for i, L in enumerate(self.layers):
+            where = f"config.json: layers[{i}]"
+            if L.kind not in self.KINDS:
+                raise ConfigError(f"{where}.type {L.kind!r}: known are {', '.join(self.KINDS)}")
+            if L.heads <= 0 or L.vdim <= 0:
+                raise ConfigError(f"{where}.mixer: heads and vdim must be positive")
+            if L.kind in ("attention", "retention"):
+                if L.dim <= 0:
+                    raise ConfigError(f"{where}.mixer.dim must be positive")
+                if L.rot_dims < 0 or L.rot_dims % 2 or L.rot_dims > L.dim or (L.rot_dims and not L.rot_base > 1):
+                    raise ConfigError(f"{where}.mixer.rot: dims ({L.rot_dims}) must be even and at most dim ({L.dim}), base above 1")
+            if L.kind == "attention":
+                if L.kv_heads <= 0 or L.heads % L.kv_heads:
+                    raise ConfigError(f"{where}.mixer.kv_heads ({L.kv_heads}) must divide heads ({L.heads})")
+                if not L.scale > 0 or L.window < 0 or L.conv < 0 or L.conv == 1:
+                    raise ConfigError(f"{where}.mixer: scale must be positive, mask.size not negative, conv 0 or at least 2")
+                if L.kv_from >= 0:
+                    src = self.layers[L.kv_from] if L.kv_from < i else None
+                    if src is None or src.kind != "attention" or src.kv_from >= 0:
+                        raise ConfigError(f"{where}.mixer.kv_from ({L.kv_from}) must name an earlier attention layer with keys and values of its own")
+                    if (src.kv_heads, src.dim, src.vdim, src.rot_dims, src.rot_base, src.rot_scaling) != \
+                            (L.kv_heads, L.dim, L.vdim, L.rot_dims, L.rot_base, L.rot_scaling):
+                        raise ConfigError(f"{where}.mixer: head sizes and rotation must equal those of layer {L.kv_from}, whose keys and values it reads")
+            if L.kind == "retention" and len(L.decay) != L.heads:
+                raise ConfigError(f"{where}.mixer.decay: {len(L.decay)} decays for {L.heads} heads")
+            if L.kind == "mamba2":
+                if L.state <= 0 or L.groups <= 0 or L.heads % L.groups or L.norm_groups <= 0 or (L.heads * L.vdim) % L.norm_groups:
+                    raise ConfigError(f"{where}.mixer: state, groups and norm_groups must be positive, groups divide heads and "
+                                      f"norm_groups divide heads * vdim")
+                if L.conv < 0 or L.conv == 1:
+                    raise ConfigError(f"{where}.mixer.conv must be at least 2")
+            if L.mlp_kind not in ("", "moe"):
+                raise ConfigError(f"{where}.mlp.kind {L.mlp_kind!r}: known is 'moe'")
+            if L.mlp_kind == "moe" and (L.ff <= 0 or L.experts <= 0 or not 0 < L.top <= L.experts or L.shared_ff < 0):
+                raise ConfigError(f"{where}.mlp: ff must be positive and {L.experts} experts cannot give top {L.top}")
+
+    @classmethod
+    def from_dict(cls, raw: dict[str, Any]) -> "NipudraConfig":
+        norm = raw.get("norm")
+        if not isinstance(norm, dict):
+            raise ConfigError("config.json: required key 'norm' (with 'eps') is missing")
+        layers_raw = raw.get("layers")
+        if not isinstance(layers_raw, (list, tuple)):
+            raise ConfigError("config.json: required key 'layers' is missing")
+        layers = []
+        for i, entry in enumerate(layers_raw):
+            where = f"layers[{i}]"
+            if not isinstance(entry, dict) or not isinstance(entry.get("mixer"), dict):
+                raise ConfigError(f"config.json: {where} needs 'type' and 'mixer'")
+            m, kind = entry["mixer"], str(entry.get("type"))
+            fields = dict(kind=kind, heads=_require(m, "heads"), vdim=_require(m, "vdim"))
+            rot = m.get("rot") or {}
+            if kind in ("attention", "retention"):
+                fields.update(dim=_require(m, "dim"), rot_dims=int(rot.get("dims", 0)), rot_base=float(rot.get("base", 10000.0)))
+            if kind == "attention":
+                sc = rot.get("scaling")
+                if sc is not None:
+                    if not isinstance(sc, dict):
+                        raise ConfigError(f"config.json: {where}.mixer.rot.scaling must be an object or null")
+                    sc = tuple(_require(sc, k, float) for k in ("factor", "original", "fast", "slow"))
+                mask = m.get("mask") or {}
+                kv_from = m.get("kv_from")
+                fields.update(kv_heads=int(m.get("kv_heads") or fields["heads"]), scale=_require(m, "scale", float),
+                              diff=_require(m, "diff", float), window=int(mask.get("size") or 0),
+                              kv_from=-1 if kv_from is None else int(kv_from), conv=int(m.get("conv") or 0), rot_scaling=sc)
+            elif kind == "retention":
+                decay = m.get("decay")
+                if not isinstance(decay, (list, tuple)):
+                    raise ConfigError(f"config.json: {where}.mixer.decay must be a list with one decay per head")
+                fields["decay"] = tuple(float(d) for d in decay)
+            elif kind == "mamba2":
+                fields.update(state=_require(m, "state"), groups=int(m.get("groups") or 1), conv=int(m.get("conv") or 0),
+                              norm_groups=int(m.get("norm_groups") or 1))
+            mlp = entry.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict):
+                    raise ConfigError(f"config.json: {where}.mlp must be an object or null")
+                fields["mlp_kind"] = str(mlp.get("kind", "moe"))
+                expert, router = mlp.get("expert"), mlp.get("router")
+                if not isinstance(expert, dict) or not isinstance(router, dict):
+                    raise ConfigError(f"config.json: {where}.mlp needs 'expert' and 'router'")
+                shared = mlp.get("shared") or {}
+                fields.update(ff=_require(expert, "ff"), experts=_require(router, "experts"), top=_require(router, "top"),
+                              shared_ff=int(shared.get("ff") or 0))
+            layers.append(NipudraLayer(**fields))
+        emb, side = raw.get("embedding") or {}, raw.get("token_side") or {}
+        return cls(vocab=_require(raw, "vocab"), width=_require(raw, "width"), norm_eps=_require(norm, "eps", float),
+                   layers=tuple(layers), embedding_scale=float(emb.get("scale", 1.0)), logit_scale=float(raw.get("logit_scale") or 1.0),
+                   logit_softcap=float(raw.get("logit_softcap") or 0.0), side_dim=int(side.get("dim") or 0))
+
+    def to_dict(self) -> dict[str, Any]:
+        layers = []
+        for L in self.layers:
+            rot = {"dims": L.rot_dims, "base": L.rot_base} if L.rot_dims else None
+            if L.kind == "attention":
+                mixer = {"heads": L.heads, "kv_heads": L.kv_heads, "dim": L.dim, "vdim": L.vdim, "scale": L.scale, "diff": L.diff}
+                if L.conv:
+                    mixer["conv"] = L.conv
+                if L.window:
+                    mixer["mask"] = {"size": L.window}
+                if L.kv_from >= 0:
+                    mixer["kv_from"] = L.kv_from
+                if rot:
+                    if L.rot_scaling:
+                        rot["scaling"] = dict(zip(("factor", "original", "fast", "slow"), L.rot_scaling))
+                    mixer["rot"] = rot
+            elif L.kind == "retention":
+                mixer = {"heads": L.heads, "dim": L.dim, "vdim": L.vdim, "decay": list(L.decay)}
+                if rot:
+                    mixer["rot"] = rot
+            else:
+                mixer = {"heads": L.heads, "vdim": L.vdim, "state": L.state, "groups": L.groups, "conv": L.conv,
+                         "norm_groups": L.norm_groups}
+            mlp = None
+            if L.mlp_kind == "moe":
+                mlp = {"kind": "moe", "expert": {"ff": L.ff}, "router": {"experts": L.experts, "top": L.top}}
+                if L.shared_ff:
+                    mlp["shared"] = {"ff": L.shared_ff}
+            layers.append({"type": L.kind, "mixer": mixer, "mlp": mlp})
+        out = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.norm_eps},
+               "embedding": {"scale": self.embedding_scale}, "logit_scale": self.logit_scale, "layers": layers}
+        if self.logit_softcap:
+            out["logit_softcap"] = self.logit_softcap
+        if self.side_dim:
+            out["token_side"] = {"dim": self.side_dim}
+        return out
+
+    def needs_tensor_shapes(self) -> bool:
+        return any(L.kind == "mamba2" and not L.conv for L in self.layers)
+
+    def with_tensor_shapes(self, shape_of) -> "NipudraConfig":
+        """The configuration with the sizes that only the weights give filled in; ``shape_of(name)`` returns the
+        shape of a checkpoint tensor (or None)."""
+        layers = []
+        for i, L in enumerate(self.layers):
+            if L.kind == "mamba2" and not L.conv:
+                shape = shape_of(f"l{i}.mix.conv")
+                if shape is None or len(shape) != 2:
+                    raise ConfigError(f"config.json: layers[{i}] gives no conv and the weights hold no l{i}.mix.conv to read it from")
+                L = dataclasses.replace(L, conv=int(shape[1]))
+            layers.append(L)
+        return dataclasses.replace(self, layers=tuple(layers))

@@ -84,4 +84,4 @@ def _ensure_builtin() -> None:
     global _builtin_done
     if not _builtin_done:
         _builtin_done = True
-        from ..models import modovik, pivinex, qwen2, tekarax  # noqa: F401
+        from ..models import modovik, nipudra, pivinex, qwen2, tekarax  # noqa: F401

@@ -498,8 +498,8 @@ PYRE_API int pyre_add_row_vector(float* x, const float* v, long long n_rows, int
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void gated_norm_kernel(const T* y, const float* partials, int n_partials, long long partial_stride,
-                                  const float* y_bias, const T* g, const float* g_bias, const float* w, float* out, int H,
-                                  float eps, int center) {
+                                  const float* y_bias, const T* g, const float* g_bias, const float* w, const float* out_bias,
+                                  float* out, int H, float eps, int center) {
     extern __shared__ float row_smem[];   // [H]
     __shared__ float scratch[33];
     pdl_trigger();
@@ -523,22 +523,24 @@ __global__ void gated_norm_kernel(const T* y, const float* partials, int n_parti
         ss = fmaf(d, d, ss);
     }
     const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x)
-        out[(size_t)r * H + i] = __fmul_rn(__fmul_rn(row_smem[i] - mean, rstd), w[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float o = __fmul_rn(__fmul_rn(row_smem[i] - mean, rstd), w[i]);
+        out[(size_t)r * H + i] = out_bias ? __fadd_rn(o, out_bias[i]) : o;
+    }
 }
 
 PYRE_API int pyre_gated_norm(const void* y, const float* partials, int n_partials, long long partial_stride,
-                             const float* y_bias, const void* gate, const float* gate_bias, const float* weight, float* out,
-                             int n_rows, int H, float eps, int center, int dtype, cudaStream_t stream) {
+                             const float* y_bias, const void* gate, const float* gate_bias, const float* weight,
+                             const float* out_bias, float* out, int n_rows, int H, float eps, int center, int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if ((y == nullptr) == (partials == nullptr) || (partials && n_partials < 1) || H <= 0 || !weight || !out) return PYRE_ERR_BAD_ARG;
     const size_t smem = (size_t)H * sizeof(float);
     if (smem > 48 * 1024) return PYRE_ERR_UNSUPPORTED;
     const int threads = min(512, max(32, ((H / 4 + 31) / 32) * 32));
     if (dtype == PYRE_BF16)
-        pyre_launch(gated_norm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, (const __nv_bfloat16*)y, partials, n_partials, partial_stride, y_bias, (const __nv_bfloat16*)gate, gate_bias, weight, out, H, eps, center);
+        pyre_launch(gated_norm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, (const __nv_bfloat16*)y, partials, n_partials, partial_stride, y_bias, (const __nv_bfloat16*)gate, gate_bias, weight, out_bias, out, H, eps, center);
     else if (dtype == PYRE_F32)
-        pyre_launch(gated_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, (const float*)y, partials, n_partials, partial_stride, y_bias, (const float*)gate, gate_bias, weight, out, H, eps, center);
+        pyre_launch(gated_norm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, (const float*)y, partials, n_partials, partial_stride, y_bias, (const float*)gate, gate_bias, weight, out_bias, out, H, eps, center);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;

@@ -375,12 +375,14 @@ PYRE_API int pyre_grouped_linear(const void* x, long long x_row_stride, long lon
 // [n_out, H]; h in the activation dtype), scores s = softmax(z), choice scores s + correction; the `top` outputs
 // with the largest choice scores are chosen (the lowest index wins a tie), and each chosen output's weight is its
 // plain score s times `scale` (not renormalised).  `sigmoid` != 0: the scores are s = sigmoid(z), each output by itself,
-// instead of the softmax.  One block per token, one warp per output in turn.
+// instead of the softmax.  `bias` (fp32 [n_out] or null) is added to the logits before anything else.  `renorm` != 0: the
+// chosen outputs' weights are divided by their sum (with softmax scores: the softmax over the chosen logits alone).
+// One block per token, one warp per output in turn.
 //   idx_out [T, top] int32, weight_out [T, top] fp32
 // ---------------------------------------------------------------------------
 template <typename T>
-__global__ void route_kernel(const T* h, const float* w, const float* correction, int* idx_out, float* weight_out, int H,
-                             int n_out, int top, float scale, int sigmoid) {
+__global__ void route_kernel(const T* h, const float* w, const float* correction, const float* bias, int* idx_out,
+                             float* weight_out, int H, int n_out, int top, float scale, int sigmoid, int renorm) {
     extern __shared__ float z_smem[];   // [n_out] logits, then scores; [n_out] choice scores
     pdl_trigger();
     pdl_wait();
@@ -405,7 +407,7 @@ __global__ void route_kernel(const T* h, const float* w, const float* correction
             for (int i = lane; i < H; i += 32) acc[0] = fmaf(to_f32<T>(hr[i]), wr[i], acc[0]);
         }
         const float sum = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
-        if (lane == 0) z[e] = sum;
+        if (lane == 0) z[e] = bias ? __fadd_rn(sum, bias[e]) : sum;
     }
     __syncthreads();
     if (warp == 0) {
@@ -451,11 +453,16 @@ __global__ void route_kernel(const T* h, const float* w, const float* correction
             }
             __syncwarp();
         }
+        if (renorm && lane == 0) {
+            float total = 0.f;
+            for (int k = 0; k < top; ++k) total += weight_out[(size_t)t * top + k];
+            for (int k = 0; k < top; ++k) weight_out[(size_t)t * top + k] = weight_out[(size_t)t * top + k] / total;
+        }
     }
 }
 
-PYRE_API int pyre_route(const void* h, const float* w, const float* correction, int* idx_out, float* weight_out, int n_tokens,
-                        int H, int n_out, int top, float scale, int sigmoid, int dtype, cudaStream_t stream) {
+PYRE_API int pyre_route(const void* h, const float* w, const float* correction, const float* bias, int* idx_out, float* weight_out,
+                        int n_tokens, int H, int n_out, int top, float scale, int sigmoid, int renorm, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (H <= 0 || n_out <= 0 || top <= 0 || top > n_out) return PYRE_ERR_BAD_ARG;
     const size_t smem = (size_t)2 * n_out * sizeof(float);
@@ -463,10 +470,10 @@ PYRE_API int pyre_route(const void* h, const float* w, const float* correction, 
     const int threads = n_tokens >= 512 ? 256 : 1024;      // few tokens: more warps per token's outputs
     if (dtype == PYRE_BF16)
         pyre_launch(route_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), smem, stream, (const __nv_bfloat16*)h, w, correction,
-                    idx_out, weight_out, H, n_out, top, scale, sigmoid);
+                    bias, idx_out, weight_out, H, n_out, top, scale, sigmoid, renorm);
     else if (dtype == PYRE_F32)
-        pyre_launch(route_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream, (const float*)h, w, correction, idx_out,
-                    weight_out, H, n_out, top, scale, sigmoid);
+        pyre_launch(route_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream, (const float*)h, w, correction, bias, idx_out,
+                    weight_out, H, n_out, top, scale, sigmoid, renorm);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;

@@ -18,14 +18,14 @@ __device__ __forceinline__ float branch_at(const T* y, const float* parts, int n
 // ---------------------------------------------------------------------------
 // v      = x[src] + (s0 * b0[src] + s1 * b1[src])      src = rows[r] or r; a branch may be absent
 // x[src] = v                                            (update_x, without rows)
-// out[r] = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * w      activation dtype, or fp32 when out_f32
+// out[r] = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * w (+ bias)      activation dtype, or fp32 when out_f32
 // One block per row; the row waits in shared memory between the passes.  The block size depends on H only, so a
 // row's sums are added in the same order whatever the batch holds.
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void add_layernorm_kernel(float* x, const T* y0, const float* p0, int n0, const float* s0, const T* y1,
                                      const float* p1, int n1, const float* s1, long long part_stride, const float* w,
-                                     void* out, int out_f32, const int* rows, int H, float eps, int update_x) {
+                                     const float* bias, void* out, int out_f32, const int* rows, int H, float eps, int update_x) {
     extern __shared__ float row_smem[];   // [H]
     __shared__ float scratch[33];
     pdl_trigger();
@@ -56,7 +56,8 @@ __global__ void add_layernorm_kernel(float* x, const T* y0, const float* p0, int
     }
     const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float o = __fmul_rn(__fmul_rn(row_smem[i] - mean, rstd), w[i]);
+        float o = __fmul_rn(__fmul_rn(row_smem[i] - mean, rstd), w[i]);
+        if (bias) o = __fadd_rn(o, bias[i]);
         if (out_f32) ((float*)out)[(size_t)r * H + i] = o;
         else ((T*)out)[(size_t)r * H + i] = from_f32<T>(o);
     }
@@ -64,7 +65,7 @@ __global__ void add_layernorm_kernel(float* x, const T* y0, const float* p0, int
 
 PYRE_API int pyre_add_layernorm(float* x, const void* y0, const float* p0, int n0, const float* s0, const void* y1,
                                 const float* p1, int n1, const float* s1, long long part_stride, const float* weight,
-                                void* out, int out_f32, const int* rows, int n_rows, int H, float eps, int update_x,
+                                const float* bias, void* out, int out_f32, const int* rows, int n_rows, int H, float eps, int update_x,
                                 int dtype, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || (size_t)H * sizeof(float) > 48 * 1024) return PYRE_ERR_UNSUPPORTED;
@@ -74,10 +75,10 @@ PYRE_API int pyre_add_layernorm(float* x, const void* y0, const float* p0, int n
     const size_t smem = (size_t)H * sizeof(float);
     if (dtype == PYRE_BF16)
         pyre_launch(add_layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, x, (const __nv_bfloat16*)y0, p0,
-                    n0, s0, (const __nv_bfloat16*)y1, p1, n1, s1, part_stride, weight, out, out_f32, rows, H, eps, update_x);
+                    n0, s0, (const __nv_bfloat16*)y1, p1, n1, s1, part_stride, weight, bias, out, out_f32, rows, H, eps, update_x);
     else if (dtype == PYRE_F32)
         pyre_launch(add_layernorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, (const float*)y0, p0, n0, s0,
-                    (const float*)y1, p1, n1, s1, part_stride, weight, out, out_f32, rows, H, eps, update_x);
+                    (const float*)y1, p1, n1, s1, part_stride, weight, bias, out, out_f32, rows, H, eps, update_x);
     else return PYRE_ERR_BAD_ARG;
     PYRE_LAUNCH_CHECK();
     return 0;

@@ -41,6 +41,7 @@ LIBRARIES = {
     "latent_attention": "latent_attention.cu",
     "grouped": "grouped.cu",
     "wkv": "wkv.cu",
+    "seqmix": "seqmix.cu",
 }
 
 HEADERS = ["common.cuh", "attention_mma_noalloc.h"]

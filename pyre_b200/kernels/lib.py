@@ -52,12 +52,12 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_head_gate": ("blockops", [P, I, P, LL, I, P, P, P, I, I, I, I, P]),
     "pyre_bias_act": ("blockops", [P, P, P, LL, I, I, I, P]),
     "pyre_add_row_vector": ("blockops", [P, P, LL, I, P]),
-    "pyre_gated_norm": ("blockops", [P, P, I, LL, P, P, P, P, P, I, I, F, I, I, P]),
+    "pyre_gated_norm": ("blockops", [P, P, I, LL, P, P, P, P, P, P, I, I, F, I, I, P]),
     "pyre_token_shift_mix": ("wkv", [P, P, LL, LL, P, P, P, P, P, I, I, I, I, P]),
     "pyre_wkv_scan": ("wkv", [P, P, P, P, P, P, P, P, P, LL, LL, P, P, P, P, P, I, I, I, I, I, F, I, P]),
     "pyre_linear_attention_scan": ("linear_attention", [P, LL, I, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P]),
     "pyre_linear_attention_chunked": ("linear_attention", [P, LL, I, I, I, P, P, P, P, P, I, I, I, I, I, I, I, P]),
-    "pyre_add_layernorm": ("parallel_block", [P, P, P, I, P, P, P, I, P, LL, P, P, I, P, I, I, F, I, I, P]),
+    "pyre_add_layernorm": ("parallel_block", [P, P, P, I, P, P, P, I, P, LL, P, P, P, I, P, I, I, F, I, I, P]),
     "pyre_scaled_sum": ("parallel_block", [P, P, I, P, P, P, I, P, LL, P, I, I, I, P]),
     "pyre_act_mul": ("parallel_block", [P, P, I, I, I, I, P]),
     "pyre_latent_prepare": ("latent_attention", [P, P, I, LL, I, I, I, I, I, I, I, P, P, F, P, P, P, P, P, I, I, LL, I, I, P, P]),
@@ -65,10 +65,18 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_latent_attention_exact": ("latent_attention", [P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, LL, P, P]),
     "pyre_latent_attention_mma": ("latent_attention", [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, F, I, I, LL, P, P]),
     "pyre_grouped_linear": ("grouped", [P, LL, LL, P, LL, P, LL, LL, P, P, P, I, I, I, I, I, I, I, I, P]),
-    "pyre_route": ("grouped", [P, P, P, P, P, I, I, I, I, F, I, I, P]),
+    "pyre_route": ("grouped", [P, P, P, P, P, P, I, I, I, I, F, I, I, I, P]),
     "pyre_scale_to_places": ("grouped", [P, P, P, P, I, I, I, I, P]),
     "pyre_group_pairs": ("grouped", [P, I, I, I, P, P, P, P]),
     "pyre_combine_pairs": ("grouped", [P, P, P, P, P, I, I, I, I, P]),
+    "pyre_scale_cap": ("seqmix", [P, LL, F, F, P]),
+    "pyre_short_conv": ("seqmix", [P, LL, I, P, P, P, P, LL, LL, P, P, P, P, I, I, I, I, I, I, P]),
+    "pyre_ssm_scan": ("seqmix", [P, LL, P, LL, I, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, I, P]),
+    "pyre_group_norm_gate": ("seqmix", [P, P, LL, I, I, I, P, F, P, I, I, I, F, I, P]),
+    "pyre_diff_combine": ("seqmix", [P, I, F, F, P, I, I, I, I, F, I, P]),
+    "pyre_rotate_heads": ("seqmix", [P, LL, I, P, P, I, I, I, I, F, I, P]),
+    "pyre_side_gate": ("seqmix", [P, P, LL, I, P, I, P, I, I, I, P, P]),
+    "pyre_token_gate_add": ("seqmix", [P, P, P, P, I, I, I, I, P]),
 }
 
 _ERRORS = {100001: "bad argument", 100002: "unsupported size"}
@@ -96,6 +104,8 @@ DEFAULT_CLASS = {
     "pyre_route": "router", "pyre_group_pairs": "router", "pyre_combine_pairs": "router", "pyre_scale_to_places": "router",
     "pyre_head_gate": "gate", "pyre_bias_act": "activation", "pyre_add_row_vector": "norm", "pyre_gated_norm": "norm",
     "pyre_token_shift_mix": "recurrence", "pyre_wkv_scan": "recurrence",
+    "pyre_scale_cap": "scale", "pyre_short_conv": "short_conv", "pyre_ssm_scan": "recurrence", "pyre_group_norm_gate": "gate",
+    "pyre_diff_combine": "gate", "pyre_rotate_heads": "rotary+write", "pyre_side_gate": "activation", "pyre_token_gate_add": "router",
 }
 
 

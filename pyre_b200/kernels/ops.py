@@ -1286,11 +1286,11 @@ def add_row_vector(x: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
 
 def gated_norm(y: "torch.Tensor | PartialSums | DeferredProduct", y_bias: "torch.Tensor | None", gate: "torch.Tensor | None",
                gate_bias: "torch.Tensor | None", weight: torch.Tensor, eps: float, act_dtype: torch.dtype,
-               center: bool = True) -> torch.Tensor:
+               center: bool = True, out_bias: "torch.Tensor | None" = None) -> torch.Tensor:
     """norm((y + y_bias) * sigmoid(gate + gate_bias)) * weight per row, as fp32 [T, H]: a branch's output (activation
     dtype, or fp32 partial sums that the kernel adds) gated element by element and normed, ready to be added to the
     stream.  ``center``: a layer norm without bias (mean taken off, variance of the deviations); else an RMS norm.
-    ``gate`` None: no gate."""
+    ``gate`` None: no gate.  ``out_bias`` fp32 [H]: added after the gain (a norm with a bias)."""
     _check(weight, "weight", torch.float32, 1)
     H = weight.shape[0]
     if isinstance(y, DeferredProduct):
@@ -1307,7 +1307,7 @@ def gated_norm(y: "torch.Tensor | PartialSums | DeferredProduct", y_bias: "torch
         T, device = y.shape[0], y.device
         if y.shape[1] != H:
             raise ValueError(f"branch output rows of {y.shape[1]}, norm weight of {H}")
-    for b, name in ((y_bias, "y_bias"), (gate_bias, "gate_bias")):
+    for b, name in ((y_bias, "y_bias"), (gate_bias, "gate_bias"), (out_bias, "out_bias")):
         if b is not None:
             _check(b, name, torch.float32, 1)
             if b.shape[0] != H:
@@ -1320,7 +1320,8 @@ def gated_norm(y: "torch.Tensor | PartialSums | DeferredProduct", y_bias: "torch
         raise UnsupportedSize(f"rows of {H}: the gated norm takes up to 12,288 entries")
     out = torch.empty((T, H), dtype=torch.float32, device=device)
     lib.call("pyre_gated_norm", _ptr(y), _ptr(parts), n_parts, stride, _ptr(y_bias), _ptr(gate),
-             _ptr(gate_bias) if gate is not None else None, weight.data_ptr(), out.data_ptr(), T, H, float(eps), int(bool(center)),
+             _ptr(gate_bias) if gate is not None else None, weight.data_ptr(), _ptr(out_bias), out.data_ptr(), T, H, float(eps),
+             int(bool(center)),
              _dt(act_dtype), _stream())
     return out
 
@@ -1467,9 +1468,9 @@ class ScaledSum:
 
 def add_layernorm(x: torch.Tensor, delta: "ScaledSum | torch.Tensor | PartialSums | None", weight: torch.Tensor, eps: float,
                   out_dtype: torch.dtype, rows: "torch.Tensor | None" = None, update_x: bool = True,
-                  act_dtype: "torch.dtype | None" = None) -> torch.Tensor:
-    """out[r] = layernorm(x[src] + delta[src]) * weight with src = rows[r] (or r): the mean is taken off, the
-    variance is the mean squared deviation, no bias.  ``x`` is the fp32 residual stream [T, H]; with ``update_x``
+                  act_dtype: "torch.dtype | None" = None, bias: "torch.Tensor | None" = None) -> torch.Tensor:
+    """out[r] = layernorm(x[src] + delta[src]) * weight (+ bias) with src = rows[r] (or r): the mean is taken off, the
+    variance is the mean squared deviation; ``bias`` fp32 [H] or None.  ``x`` is the fp32 residual stream [T, H]; with ``update_x``
     (and no ``rows``) the sum is written back to it.  ``delta``: a ``ScaledSum`` (each term times its gain), a
     plain branch output or partial sums (gain one), or None.  ``out_dtype`` float32 with bfloat16 activations
     (``act_dtype``) gives the normalised rows in fp32: a norm applied to the stream itself."""
@@ -1479,6 +1480,10 @@ def add_layernorm(x: torch.Tensor, delta: "ScaledSum | torch.Tensor | PartialSum
     act = act_dtype or out_dtype
     if weight.shape[0] != H:
         raise ValueError(f"norm weight has {weight.shape[0]} entries, rows have {H}")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != H:
+            raise ValueError(f"norm bias has {bias.shape[0]} entries, rows have {H}")
     if H * 4 > 48 * 1024:
         raise UnsupportedSize(f"layer norm over rows of {H}: the kernel holds a row of at most 12,288 in shared memory")
     if delta is not None and not isinstance(delta, ScaledSum):
@@ -1494,7 +1499,7 @@ def add_layernorm(x: torch.Tensor, delta: "ScaledSum | torch.Tensor | PartialSum
         n_rows, update_x = rows.shape[0], False
     out = torch.empty((n_rows, H), dtype=out_dtype, device=x.device)
     a = args
-    lib.call("pyre_add_layernorm", x.data_ptr(), a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], stride, weight.data_ptr(), out.data_ptr(),
+    lib.call("pyre_add_layernorm", x.data_ptr(), a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], stride, weight.data_ptr(), _ptr(bias), out.data_ptr(),
              int(out_dtype == torch.float32 and act != torch.float32), _ptr(rows), n_rows, H, float(eps),
              int(bool(update_x and delta is not None)), _dt(act), _stream())
     return out
@@ -1661,10 +1666,12 @@ def expert_linear(x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, src: 
     return out
 
 
-def route(h: torch.Tensor, w: torch.Tensor, correction: "torch.Tensor | None", top: int, scale: float, sigmoid: bool = False):
-    """Router of a routed feed-forward: fp32 logits w h over all router outputs, softmax scores s (``sigmoid``: each
-    output's own sigmoid instead); the ``top`` outputs with the largest s + correction are chosen (lowest index on
-    ties), weights s * scale.
+def route(h: torch.Tensor, w: torch.Tensor, correction: "torch.Tensor | None", top: int, scale: float, sigmoid: bool = False,
+          bias: "torch.Tensor | None" = None, renormalise: bool = False):
+    """Router of a routed feed-forward: fp32 logits w h (+ ``bias``) over all router outputs, softmax scores s
+    (``sigmoid``: each output's own sigmoid instead); the ``top`` outputs with the largest s + correction are chosen
+    (lowest index on ties), weights s * scale; ``renormalise``: divided by their sum over the chosen (with softmax
+    scores that is the softmax over the chosen logits alone).
     Returns (idx int32 [T, top], weight fp32 [T, top])."""
     _check(h, "h", dim=2)
     _check(w, "w", torch.float32, 2)
@@ -1676,12 +1683,16 @@ def route(h: torch.Tensor, w: torch.Tensor, correction: "torch.Tensor | None", t
         _check(correction, "correction", torch.float32, 1)
         if correction.shape[0] != n_out:
             raise ValueError("one correction per router output")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != n_out:
+            raise ValueError("one bias per router output")
     if n_out * 8 > 48 * 1024:
         raise UnsupportedSize(f"{n_out} router outputs: the kernel takes up to 6,144")
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     weight = torch.empty((T, top), dtype=torch.float32, device=h.device)
-    lib.call("pyre_route", h.data_ptr(), w.data_ptr(), _ptr(correction), idx.data_ptr(), weight.data_ptr(), T, H, n_out, int(top),
-             float(scale), int(bool(sigmoid)), _dt(h.dtype), _stream())
+    lib.call("pyre_route", h.data_ptr(), w.data_ptr(), _ptr(correction), _ptr(bias), idx.data_ptr(), weight.data_ptr(), T, H, n_out,
+             int(top), float(scale), int(bool(sigmoid)), int(bool(renormalise)), _dt(h.dtype), _stream())
     return idx, weight
 
 
@@ -1870,3 +1881,174 @@ def latent_attention(ctx, qa: torch.Tensor, cache_layer: torch.Tensor, block_tab
     span = ctx.max_context if not window else min(ctx.max_context, window + tq)
     return latent_attention_mma(qa, cache_layer, block_table, ctx.cu_seqlens, ctx.positions, n_tiles, rank, scale, window,
                                 latent_attention_splits(n_tiles, nh, rank, span, row))
+
+
+# ---------------------------------------------------------------------------------- short histories and recurrent states
+def scale_cap(x: torch.Tensor, scale: float = 1.0, cap: float = 0.0) -> torch.Tensor:
+    """x = scale * x, then cap * tanh(x / cap) where ``cap`` > 0; fp32, in place (a scaled embedding, rotary tables
+    with an amplitude, logits with a factor and a soft cap)."""
+    _check(x, "x", torch.float32)
+    lib.call("pyre_scale_cap", x.data_ptr(), x.numel(), float(scale), float(cap), _stream())
+    return x
+
+
+def short_conv(inp: torch.Tensor, col: int, n_ch: int, weight: torch.Tensor, bias: "torch.Tensor | None", state_layer: torch.Tensor,
+               state_off: int, slots: torch.Tensor, seq_of_token: torch.Tensor, cu_seqlens: torch.Tensor, silu: bool = False,
+               in_bias: "torch.Tensor | None" = None) -> torch.Tensor:
+    """A short causal convolution over time per channel, continuing each request's history:
+    y[t, c] = act(bias[c] + sum_j weight[c, j] u[t - taps + 1 + j, c]) with u the ``n_ch`` columns of ``inp`` from
+    ``col``; the last tap is the token's own.  ``state_layer`` [slots, floats] fp32 holds, ``state_off`` floats into
+    slot ``slots[b]``, entry b's last ``taps - 1`` inputs [taps - 1, n_ch] (oldest first; zeros when a request begins)
+    and is left moved on by the step's tokens.  ``in_bias`` fp32 [n_ch]: added to every input as it is read from ``inp``
+    (a projection's bias; the history holds inputs with it).  Returns [T, n_ch] in the dtype of ``inp``."""
+    _check(inp, "inp", dim=2)
+    _check(weight, "weight", torch.float32, 2)
+    _check(state_layer, "state_layer", torch.float32, 2)
+    _check(slots, "slots", torch.int32, 1)
+    _check(seq_of_token, "seq_of_token", torch.int32, 1)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    T, W = inp.shape
+    taps = weight.shape[1]
+    n_seqs = cu_seqlens.shape[0] - 1
+    if weight.shape[0] != n_ch or col < 0 or col + n_ch > W or taps < 1:
+        raise ValueError("the convolution's channels do not lie inside the row, or its weight does not match them")
+    if state_off < 0 or state_off + (taps - 1) * n_ch > state_layer.shape[1] or slots.shape[0] < n_seqs or seq_of_token.shape[0] < T:
+        raise ValueError("the history does not lie inside the state slot, or slots do not match the batch")
+    for v, name in ((bias, "bias"), (in_bias, "in_bias")):
+        if v is not None:
+            _check(v, name, torch.float32, 1)
+            if v.shape[0] != n_ch:
+                raise ValueError(f"{name}: one entry per channel")
+    out = torch.empty((T, n_ch), dtype=inp.dtype, device=inp.device)
+    lib.call("pyre_short_conv", inp.data_ptr(), W, int(col), _ptr(in_bias), weight.data_ptr(), _ptr(bias), state_layer.data_ptr(),
+             state_layer.shape[1], int(state_off), slots.data_ptr(), seq_of_token.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(),
+             T, n_seqs, int(n_ch), int(taps), int(bool(silu)), _dt(inp.dtype), _stream())
+    return out
+
+
+SSM_MAX_STATE = 256
+
+
+def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state_layer: torch.Tensor, slots: torch.Tensor, cu_seqlens: torch.Tensor, n_heads: int, n_groups: int, p_dim: int,
+             n_state: int) -> torch.Tensor:
+    """The selective state-space recurrence over the step's entries, continuing each request's state.  Per head h of
+    group h // (n_heads / n_groups), with x_t [p_dim], B_t and C_t [n_state] columns of ``xbc`` ([x: heads * p_dim |
+    B: groups * n_state | C: groups * n_state]) and the raw step size column ``dt_col + h`` of ``proj``:
+    dt = softplus(raw + dt_bias), S_t = exp(-exp(a_log) dt) S_(t-1) + dt B_t x_t^T, y_t = S_t^T C_t + d_skip x_t.
+    ``state_layer`` [slots, floats] fp32 holds S [heads, n_state, p_dim] at the start of slot ``slots[b]``.
+    Token by token in fp32, bit-identical under any cutting.  Returns fp32 [T, heads * p_dim]."""
+    _check(xbc, "xbc", dim=2)
+    _check(proj, "proj", xbc.dtype, 2)
+    _check(state_layer, "state_layer", torch.float32, 2)
+    _check(slots, "slots", torch.int32, 1)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    T = xbc.shape[0]
+    n_seqs = cu_seqlens.shape[0] - 1
+    for v, name in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip")):
+        _check(v, name, torch.float32, 1)
+        if v.shape[0] != n_heads:
+            raise ValueError(f"{name}: one entry per head")
+    if n_state > SSM_MAX_STATE:
+        raise UnsupportedSize(f"a state of {n_state} rows per head: the recurrence takes up to {SSM_MAX_STATE}")
+    if n_heads % n_groups or xbc.shape[1] != n_heads * p_dim + 2 * n_groups * n_state or proj.shape[0] != T \
+            or dt_col < 0 or dt_col + n_heads > proj.shape[1]:
+        raise ValueError("x, B, C or the step sizes do not match the heads and groups")
+    if n_heads * n_state * p_dim > state_layer.shape[1] or slots.shape[0] < n_seqs:
+        raise ValueError("the state does not lie inside the slot, or slots do not match the batch")
+    y = torch.empty((T, n_heads * p_dim), dtype=torch.float32, device=xbc.device)
+    lib.call("pyre_ssm_scan", xbc.data_ptr(), xbc.shape[1], proj.data_ptr(), proj.shape[1], int(dt_col), dt_bias.data_ptr(),
+             a_log.data_ptr(), d_skip.data_ptr(), state_layer.data_ptr(), state_layer.shape[1], slots.data_ptr(),
+             cu_seqlens.data_ptr(), y.data_ptr(), T, n_seqs, int(n_heads), int(n_groups), int(p_dim), int(n_state), _dt(xbc.dtype),
+             _stream())
+    return y
+
+
+GATE_ACTIVATIONS = {"silu": 1, "sigmoid": 2}
+
+
+def group_norm_gate(y: torch.Tensor, groups: int, weight: "torch.Tensor | None", eps: float, proj: "torch.Tensor | None", g_col: int,
+                    out_dtype: torch.dtype, gate: str = "silu", gate_first: bool = False, post: float = 1.0) -> torch.Tensor:
+    """A unit norm over each of ``groups`` equal parts of the rows of fp32 ``y`` [T, W], times ``weight`` (fp32 [W] or
+    None) and ``post``, with a gate act(proj[t, g_col:g_col + W]) (``gate`` silu or sigmoid; ``proj`` None: none) that
+    multiplies ``y`` BEFORE the norm (``gate_first``) or its result.  Returns [T, W] in ``out_dtype``."""
+    _check(y, "y", torch.float32, 2)
+    T, W = y.shape
+    if groups <= 0 or W % groups:
+        raise ValueError(f"rows of {W} do not divide into {groups} equal parts")
+    if weight is not None:
+        _check(weight, "weight", torch.float32, 1)
+        if weight.shape[0] != W:
+            raise ValueError(f"norm weight has {weight.shape[0]} entries, rows have {W}")
+    if gate not in GATE_ACTIVATIONS:
+        raise UnsupportedSize(f"gate {gate!r}: implemented are {sorted(GATE_ACTIVATIONS)}")
+    if proj is not None:
+        _check(proj, "proj", out_dtype, 2)
+        if proj.shape[0] != T or g_col < 0 or g_col + W > proj.shape[1]:
+            raise ValueError("the gate does not lie inside the projection row")
+    out = torch.empty((T, W), dtype=out_dtype, device=y.device)
+    lib.call("pyre_group_norm_gate", y.data_ptr(), _ptr(proj), proj.shape[1] if proj is not None else 0,
+             int(g_col) if proj is not None else -1, GATE_ACTIVATIONS[gate], int(bool(gate_first)), _ptr(weight), float(post),
+             out.data_ptr(), T, W, int(groups), float(eps), _dt(out_dtype), _stream())
+    return out
+
+
+def diff_combine(a: torch.Tensor, a_dim: int, lam: float, post: float, n_heads: int, n_kv_heads: int, v_dim: int, eps: float) -> torch.Tensor:
+    """Two softmax maps per head over the same values: o = a1 - lam * a2, then o / sqrt(mean(o^2) + eps) * post over
+    the head's ``v_dim`` values.  ``a`` [T, 2 * n_heads * a_dim] holds the maps' sums grouped by key/value head: for
+    head h = g * rep + r (rep = n_heads / n_kv_heads) map m is row (g * 2 + m) * rep + r of ``a_dim`` >= ``v_dim``
+    columns.  Returns [T, n_heads * v_dim] in the heads' own order."""
+    _check(a, "a", dim=2)
+    T = a.shape[0]
+    if n_heads % n_kv_heads or a.shape[1] != 2 * n_heads * a_dim or a_dim < v_dim:
+        raise ValueError("the maps do not match the heads")
+    out = torch.empty((T, n_heads * v_dim), dtype=a.dtype, device=a.device)
+    lib.call("pyre_diff_combine", a.data_ptr(), int(a_dim), float(lam), float(post), out.data_ptr(), T, int(n_heads), int(n_kv_heads),
+             int(v_dim), float(eps), _dt(a.dtype), _stream())
+    return out
+
+
+def rotate_heads(proj: torch.Tensor, col: int, n_heads: int, dim: int, cos: "torch.Tensor | None", sin: "torch.Tensor | None",
+                 rotary_dim: int, factor: float = 1.0) -> torch.Tensor:
+    """In place on ``proj`` [T, W]: the ``n_heads`` heads of ``dim`` columns from ``col`` turn their pairs
+    (i, i + rotary_dim / 2) by the token's angle (cos, sin fp32 [T, rotary_dim / 2]) and are multiplied by ``factor``."""
+    _check(proj, "proj", dim=2)
+    T, W = proj.shape
+    if col < 0 or col + n_heads * dim > W or rotary_dim % 2 or not 0 <= rotary_dim <= dim:
+        raise ValueError("the heads do not lie inside the row, or the rotated dims do not fit a head")
+    if rotary_dim:
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if tuple(cos.shape) != (T, rotary_dim // 2) or tuple(sin.shape) != (T, rotary_dim // 2):
+            raise ValueError(f"cos/sin must be [{T}, {rotary_dim // 2}]")
+    lib.call("pyre_rotate_heads", proj.data_ptr(), W, int(col), _ptr(cos) if rotary_dim else None, _ptr(sin) if rotary_dim else None,
+             T, int(n_heads), int(dim), int(rotary_dim), float(factor), _dt(proj.dtype), _stream())
+    return proj
+
+
+def side_gate(pre: torch.Tensor, table: torch.Tensor, col: int, token_ids: torch.Tensor, err_flag: "torch.Tensor | None" = None) -> torch.Tensor:
+    """out[t, j] = gelu_tanh(pre[t, j]) * table[token_ids[t], col + j]: a token's slice of a side table, gated."""
+    _check(pre, "pre", dim=2)
+    _check(table, "table", pre.dtype, 2)
+    _check(token_ids, "token_ids", torch.int32, 1)
+    T, dim = pre.shape
+    if token_ids.shape[0] != T or col < 0 or col + dim > table.shape[1]:
+        raise ValueError("the slice does not lie inside the table's rows, or the ids do not match the tokens")
+    out = torch.empty_like(pre)
+    lib.call("pyre_side_gate", pre.data_ptr(), table.data_ptr(), table.shape[1], int(col), token_ids.data_ptr(), table.shape[0],
+             out.data_ptr(), T, dim, _dt(pre.dtype), _ptr(err_flag), _stream())
+    return out
+
+
+def token_gate_add(acc: torch.Tensor, h: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """acc[t] += sigmoid(w . h[t]) * y[t] in place on fp32 ``acc`` [T, W]: a branch let in by one gate per token
+    (``w`` fp32 [K], ``h`` [T, K] and ``y`` [T, W] activations)."""
+    _check(acc, "acc", torch.float32, 2)
+    _check(h, "h", dim=2)
+    _check(y, "y", h.dtype, 2)
+    _check(w, "w", torch.float32, 1)
+    T, W = acc.shape
+    if h.shape[0] != T or tuple(y.shape) != (T, W) or w.shape[0] != h.shape[1]:
+        raise ValueError("acc, h, w and y do not match")
+    lib.call("pyre_token_gate_add", acc.data_ptr(), h.data_ptr(), w.data_ptr(), y.data_ptr(), T, h.shape[1], W, _dt(h.dtype), _stream())
+    return acc

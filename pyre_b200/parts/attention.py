@@ -10,6 +10,22 @@ from ..weights.specs import TensorSpec
 from .base import HeadGeometry, PagedKVSpec, Part, PartSpec, ProjectionLayout, make_part, register_part
 
 
+def attention_libraries(dtype, row_dim: int) -> list[str]:
+    """The kernel libraries that ``attend`` needs for cache rows of ``row_dim`` in ``dtype``."""
+    if dtype == torch.bfloat16 and row_dim <= ops.MMA_MAX_HEAD_DIM:
+        return ["attention_mma"] + (["attention_prefill", "attention_tc"] if row_dim in ops.PREFILL_HEAD_DIMS else [])
+    return ["attention_generic"]
+
+
+def attend(ctx, dtype, q, layer, kv, n_heads: int, n_kv_heads: int, row_dim: int, scale: float, window, sink=None):
+    """Softmax attention of every token of the step over its sequence's cached keys and values in ``layer``, by the
+    package's kernels: bfloat16 rows up to 128 on the tensor cores, everything else on the exact fp32 kernel."""
+    if dtype == torch.bfloat16 and row_dim <= ops.MMA_MAX_HEAD_DIM:
+        return ops.paged_attention_bf16(ctx, q, layer, kv.block_table, n_heads, n_kv_heads, row_dim, scale, window, sink=sink)
+    return ops.paged_attention_generic(q, layer, kv.block_table, ctx.seq_of_token, ctx.positions, n_heads, n_kv_heads, row_dim,
+                                       scale, window, sink=sink)
+
+
 class Attention(Part):
     """q, k, v projections (stacked into one product); the position encoding (a sub-part, which adds the
     bias, encodes positions into q and k in its own way and writes keys and values to the pages of this
@@ -150,12 +166,7 @@ class Attention(Part):
         libs = ["elementwise"]      # the position encoding, a sub-part, names its own
         if self.general:
             libs.append("blockops")
-        if self.dtype == torch.bfloat16 and self.row_dim <= ops.MMA_MAX_HEAD_DIM:
-            libs.append("attention_mma")
-            if self.row_dim in ops.PREFILL_HEAD_DIMS:
-                libs += ["attention_prefill", "attention_tc"]
-        else:
-            libs.append("attention_generic")
+        libs += attention_libraries(self.dtype, self.row_dim)
         libs.append("gemm_f32" if self.dtype == torch.float32 else "gemm_tc")
         return libs
 
@@ -170,12 +181,8 @@ class Attention(Part):
         return (ops.attention_splits(n_rows, n_rows, self.n_heads, self.n_kv_heads, max_context, self.window),)
 
     def _attend(self, ctx, q, layer, kv):
-        if self.dtype == torch.bfloat16 and self.row_dim <= ops.MMA_MAX_HEAD_DIM:
-            return ops.paged_attention_bf16(ctx, q, layer, kv.block_table, self.n_heads, self.n_kv_heads, self.row_dim,
-                                            self.scale, self.window, sink=self.sink)
-        # float32 and head sizes above 128: the exact fp32-arithmetic kernel
-        return ops.paged_attention_generic(q, layer, kv.block_table, ctx.seq_of_token, ctx.positions, self.n_heads,
-                                           self.n_kv_heads, self.row_dim, self.scale, self.window, sink=self.sink)
+        return attend(ctx, self.dtype, q, layer, kv, self.n_heads, self.n_kv_heads, self.row_dim, self.scale, self.window,
+                      sink=self.sink)
 
     def _forward_general(self, ctx, h, call):
         """Projections in one product [q | k | v | gate]; norm, position encoding and the paged write by the

@@ -1,7 +1,7 @@
 """The vocabulary of model parts.
 
-A model is put together from parts of eight categories: ``embed``, ``norm``,
-``position``, ``mixer``, ``ffn``, ``block``, ``head`` and ``tail``.  A part
+A model is put together from parts of nine categories: ``embed``, ``norm``,
+``position``, ``mixer``, ``ffn``, ``block``, ``stream``, ``head`` and ``tail``.  A part
 
 * is described by data: ``PartSpec(kind, params)``; ``kind`` is looked up in the
   registry of its category, ``params`` are the sizes and constants it is built with
@@ -36,6 +36,9 @@ Interfaces by category (``ctx`` is the StepContext, T its number of tokens):
               in); a part that needs a plain tensor calls ``kernels.ops.materialize`` on it.
               Likewise a norm may hand a consumer that declares ``takes_scaled_rows``
               ``kernels.ops.ScaledRows`` instead of a tensor (see ``PreNormBlock``)
+    stream    forward(ctx, x, pending) -> (x, pending)   a step of a layer that works on the residual stream itself
+              after the sublayers (a per-layer input derived from the step's token ids); a block that has one
+              calls it last
     head      forward(ctx, h_rows) -> fp32 logits [R, vocab]
     tail      forward(ctx, x, pending) -> fp32 logits [R, vocab] at ``ctx.logit_rows``: everything after the last
               block (the built-in one: a norm over the wanted rows, then a head)
@@ -53,7 +56,7 @@ import torch
 
 from ..weights.specs import TensorSpec
 
-CATEGORIES = ("embed", "norm", "position", "mixer", "ffn", "block", "head", "tail")
+CATEGORIES = ("embed", "norm", "position", "mixer", "ffn", "block", "stream", "head", "tail")
 
 
 @dataclass(frozen=True)
@@ -165,9 +168,15 @@ class Part:
     def tensors(self) -> dict[str, TensorSpec]:
         return {}
 
+    def shared_tensors(self) -> dict[str, TensorSpec]:
+        """Checkpoint tensors that the part reads but that belong to the model as a whole (a table that every layer
+        takes a slice of): FULL checkpoint name -> ``TensorSpec``.  Several parts may name the same tensor; it is
+        read once and ``load`` gets it under its full name."""
+        return {}
+
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         """Take the tensors named by ``tensors()`` (already on the device, already in
-        their roles' dtypes)."""
+        their roles' dtypes) and by ``shared_tensors()``."""
 
     def kernel_libraries(self) -> list[str]:
         return []
@@ -253,14 +262,17 @@ def make_part(category: str, spec: PartSpec, dtype: torch.dtype, device) -> Part
 def collect_tensors(part: Part, prefix: str = "") -> dict[str, TensorSpec]:
     """Full names of a part's tensors and of its sub-parts', under ``prefix``."""
     out = {prefix + name: spec for name, spec in part.tensors().items()}
+    out.update(part.shared_tensors())
     for sub_prefix, child in part.children().items():
         out.update(collect_tensors(child, prefix + sub_prefix))
     return out
 
 
 def load_part(part: Part, tensors: Mapping[str, torch.Tensor], prefix: str = "") -> None:
-    part.load({name: tensors[prefix + name] for name, spec in part.tensors().items()
-               if prefix + name in tensors or not getattr(spec, "optional", False)})
+    own = {name: tensors[prefix + name] for name, spec in part.tensors().items()
+           if prefix + name in tensors or not getattr(spec, "optional", False)}
+    own.update({name: tensors[name] for name in part.shared_tensors()})
+    part.load(own)
     for sub_prefix, child in part.children().items():
         load_part(child, tensors, prefix + sub_prefix)
 

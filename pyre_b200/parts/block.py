@@ -182,19 +182,21 @@ class SandwichBlock(Part):
 
     The stream ``x`` is fp32.  A sublayer's gated, normed result is formed in fp32 by one kernel (``gated_output`` of
     the norm part) and travels unadded, as ``pending``, to the next norm before a sublayer, whose kernel adds it to
-    the stream while it normalises.  ``names``: the prefixes of the sub-parts' tensors and the names of the gates'
-    weights and biases."""
+    the stream while it normalises.  ``after``: a ``stream`` part that runs once the sublayers are done (a per-layer
+    input from the step's token ids); it gets the stream and what is pending.  ``names``: the prefixes of the
+    sub-parts' tensors and the names of the gates' weights and biases."""
 
     graph_safe = True
 
     DEFAULT_NAMES = {"norm1": "norm1.", "norm1b": "norm1b.", "mixer": "mixer.", "norm2": "norm2.", "norm2b": "norm2b.",
                      "ffn": "ffn.", "gate1": "gate1.weight", "gate1_bias": "gate1.bias", "gate2": "gate2.weight",
-                     "gate2_bias": "gate2.bias"}
+                     "gate2_bias": "gate2.bias", "after": "after."}
 
     def __init__(self, dtype, device, width: int, norm1: PartSpec, mixer: PartSpec, norm1b: PartSpec,
                  norm2: "PartSpec | None" = None, ffn: "PartSpec | None" = None, norm2b: "PartSpec | None" = None,
-                 gated: bool = True, names: "dict[str, str] | None" = None):
+                 gated: bool = True, names: "dict[str, str] | None" = None, after: "PartSpec | None" = None):
         super().__init__(dtype, device)
+        self.after = make_part("stream", after, dtype, device) if after is not None else None
         if len({norm2 is None, ffn is None, norm2b is None}) != 1:
             raise ValueError("a second sublayer needs its feed-forward and both of its norms")
         self.names = dict(self.DEFAULT_NAMES, **(names or {}))
@@ -215,6 +217,8 @@ class SandwichBlock(Part):
         out = {n["norm1"]: self.norm1, n["mixer"]: self.mixer, n["norm1b"]: self.norm1b}
         if self.ffn is not None:
             out.update({n["norm2"]: self.norm2, n["ffn"]: self.ffn, n["norm2b"]: self.norm2b})
+        if self.after is not None:
+            out[n["after"]] = self.after
         return out
 
     def tensors(self):
@@ -253,6 +257,8 @@ class SandwichBlock(Part):
         if self.ffn is not None:
             h = self.norm2.forward(ctx, x, delta=pending)
             pending = self._sublayer(ctx, h, self.ffn.forward(ctx, h), self.w_g2, self.b_g2, self.norm2b)
+        if self.after is not None:
+            return self.after.forward(ctx, x, pending)
         return x, pending
 
 

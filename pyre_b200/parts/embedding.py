@@ -10,15 +10,17 @@ from .base import Part, PartSpec, make_part, register_part
 
 
 class TokenEmbedding(Part):
-    """x[t] = table[token[t]], widened to the fp32 residual stream.  ``norm``: a norm part applied to the rows
-    right away (it must offer ``normalize_stream``); its tensors lie under ``norm_prefix`` after the table's name."""
+    """x[t] = table[token[t]], widened to the fp32 residual stream, times ``scale`` (in fp32).  ``norm``: a norm part
+    applied to the rows right away (it must offer ``normalize_stream``); its tensors lie under ``norm_prefix`` after
+    the table's name."""
 
     graph_safe = True
 
     def __init__(self, dtype, device, vocab: int, width: int, tensor_name: str = "weight", norm: "PartSpec | None" = None,
-                 norm_prefix: str = ".norm"):
+                 norm_prefix: str = ".norm", scale: float = 1.0):
         super().__init__(dtype, device)
         self.vocab, self.width, self.tensor_name = int(vocab), int(width), str(tensor_name)
+        self.scale = float(scale)
         self.table = None
         self.norm = make_part("norm", norm, dtype, device) if norm is not None else None
         self.norm_prefix = str(norm_prefix)
@@ -35,10 +37,12 @@ class TokenEmbedding(Part):
         self.table = tensors[self.tensor_name]
 
     def kernel_libraries(self):
-        return ["elementwise"]
+        return ["elementwise"] + (["seqmix"] if self.scale != 1.0 else [])
 
     def forward(self, ctx):
         x = ops.embedding(self.table, ctx.token_ids, err_flag=ctx.error_flag)
+        if self.scale != 1.0:
+            ops.scale_cap(x, self.scale)
         return x if self.norm is None else self.norm.normalize_stream(ctx, x)
 
 
@@ -46,13 +50,16 @@ class LinearHead(Part):
     """fp32 logits = h W^T for the rows that were asked for.  ``tied_to`` names the
     tensor (full checkpoint name) that stands in when the head's own weight is absent:
     the embedding table of a model with tied embeddings (pyre/loader.py:58-61); the
-    storage is then shared, not copied."""
+    storage is then shared, not copied.  ``logit_scale``: a factor on the logits; ``softcap`` c > 0: the scaled
+    logits become c tanh(logits / c)."""
 
     graph_safe = True
 
-    def __init__(self, dtype, device, vocab: int, width: int, tied_to: "str | None" = None, tensor_name: str = "weight"):
+    def __init__(self, dtype, device, vocab: int, width: int, tied_to: "str | None" = None, tensor_name: str = "weight",
+                 logit_scale: float = 1.0, softcap: float = 0.0):
         super().__init__(dtype, device)
         self.vocab, self.width, self.tied_to, self.tensor_name = int(vocab), int(width), tied_to, str(tensor_name)
+        self.logit_scale, self.softcap = float(logit_scale), float(softcap)
         self.weight = None
 
     def tensors(self):
@@ -62,11 +69,15 @@ class LinearHead(Part):
         self.weight = tensors[self.tensor_name]
 
     def kernel_libraries(self):
-        return ["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"]
+        return (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"]) + (["seqmix"] if self._shaped() else [])
+
+    def _shaped(self) -> bool:
+        return self.logit_scale != 1.0 or self.softcap > 0.0
 
     def forward(self, ctx, h_rows):
         with lib.section("head"):
-            return ops.linear(h_rows, self.weight, out_dtype=torch.float32)
+            logits = ops.linear(h_rows, self.weight, out_dtype=torch.float32)
+        return ops.scale_cap(logits, self.logit_scale, self.softcap) if self._shaped() else logits
 
 
 class NormHeadTail(Part):

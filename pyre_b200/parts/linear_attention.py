@@ -7,7 +7,7 @@ import torch
 
 from ..kernels import lib, ops
 from ..weights.specs import TensorSpec
-from .base import Part, StateSpec, register_part
+from .base import Part, PartSpec, StateSpec, make_part, register_part
 
 
 class DecayLinearAttention(Part):
@@ -22,6 +22,11 @@ class DecayLinearAttention(Part):
     multiplied by sigmoid(W_g h) when ``out_gate`` and projected by W_o.  The recurrence, the norm and the gate are
     computed in fp32; the four projections are one product [q | k | v | gate].
 
+    Further parameters: ``position``: the PartSpec of a rotation applied to queries and keys (per head, by the token's
+    position) before the recurrence; ``k_scale``: a factor on the keys after it; ``norm="head"``: the unit norm runs
+    over each head's ``v_head_dim`` values instead of the whole row; ``norm_weight=False``: the norm has no gain;
+    ``gate``: ``"sigmoid"`` or ``"silu"`` of W_g h.
+
     ``names``: the checkpoint's full local names of the tensors."""
 
     DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "g": "g_proj.weight",
@@ -30,8 +35,16 @@ class DecayLinearAttention(Part):
     graph_safe = True
 
     def __init__(self, dtype, device, width: int, n_heads: int, head_dim: int, v_head_dim: int, decay, eps: float,
-                 activation: "str | None" = "silu", out_gate: bool = True, names: "dict[str, str] | None" = None):
+                 activation: "str | None" = "silu", out_gate: bool = True, names: "dict[str, str] | None" = None,
+                 position: "PartSpec | None" = None, k_scale: float = 1.0, norm: str = "row", norm_weight: bool = True,
+                 gate: str = "sigmoid"):
         super().__init__(dtype, device)
+        if norm not in ("row", "head") or gate not in ("sigmoid", "silu"):
+            raise ValueError(f"norm {norm!r} / gate {gate!r}: 'row' or 'head', 'sigmoid' or 'silu'")
+        self.position = make_part("position", position, dtype, device) if position is not None else None
+        self.k_scale, self.norm, self.norm_weight, self.gate = float(k_scale), norm, bool(norm_weight), gate
+        # the plain form (a gained norm over the row, a sigmoid gate) has a kernel of its own
+        self.grouped_norm = norm == "head" or not self.norm_weight or gate != "sigmoid"
         self.names = dict(self.DEFAULT_NAMES, **(names or {}))
         self.width, self.n_heads, self.head_dim, self.v_head_dim = int(width), int(n_heads), int(head_dim), int(v_head_dim)
         decay = [float(d) for d in decay]
@@ -54,17 +67,22 @@ class DecayLinearAttention(Part):
         if self.out_gate:
             t[n["g"]] = TensorSpec((vv, self.width))
         t[n["o"]] = TensorSpec((self.width, vv))
-        t[n["norm"]] = TensorSpec((vv,), role="vector", init=("normal", 1.0, 0.1))
+        if self.norm_weight:
+            t[n["norm"]] = TensorSpec((vv,), role="vector", init=("normal", 1.0, 0.1))
         return t
+
+    def children(self):
+        return {"": self.position} if self.position is not None else {}
 
     def load(self, tensors):
         n = self.names
         stack = [tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]] + ([tensors[n["g"]]] if self.out_gate else [])
         self.w_proj = torch.cat(stack, dim=0).contiguous()
-        self.w_o, self.norm_w = tensors[n["o"]], tensors[n["norm"]]
+        self.w_o, self.norm_w = tensors[n["o"]], tensors[n["norm"]] if self.norm_weight else None
 
     def kernel_libraries(self):
-        return ["blockops", "linear_attention", "elementwise"] + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"])
+        return ["blockops", "linear_attention", "elementwise"] + (["seqmix"] if self.grouped_norm or self.position is not None
+                                                                  or self.k_scale != 1.0 else []) + (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"])
 
     def cache_spec(self):
         return None
@@ -76,10 +94,19 @@ class DecayLinearAttention(Part):
         st = ctx.state_group(call.state_group)
         with lib.section("qkv"):
             proj = ops.materialize(ops.linear(h, self.w_proj))
+        if self.position is not None or self.k_scale != 1.0:
+            cos, sin, rot = self.position.rotation(ctx, self.head_dim) if self.position is not None else (None, None, 0)
+            if rot:
+                ops.rotate_heads(proj, self.q_col, self.n_heads, self.head_dim, cos, sin, rot)
+            ops.rotate_heads(proj, self.k_col, self.n_heads, self.head_dim, cos, sin, rot, self.k_scale)
         o = ops.linear_attention(proj, self.q_col, self.k_col, self.v_col, st.buffer[call.state_layer], st.slots,
                                  ctx.cu_seqlens, self.decay, self.n_heads, self.head_dim, self.v_head_dim, self.activation,
                                  lens=ctx.cu_seqlens_host[1:] - ctx.cu_seqlens_host[:-1])
-        a = ops.rmsnorm_gate(o, self.norm_w, self.eps, proj if self.out_gate else None, self.g_col, self.dtype)
+        if self.grouped_norm:
+            a = ops.group_norm_gate(o, self.n_heads if self.norm == "head" else 1, self.norm_w, self.eps,
+                                    proj if self.out_gate else None, self.g_col, self.dtype, gate=self.gate)
+        else:
+            a = ops.rmsnorm_gate(o, self.norm_w, self.eps, proj if self.out_gate else None, self.g_col, self.dtype)
         with lib.section("o"):
             return ops.linear(a, self.w_o, partials_ok=True)
 

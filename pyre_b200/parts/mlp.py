@@ -132,8 +132,13 @@ class RoutedMLP(Part):
     ``scores="sigmoid"``: each router output's score is its own sigmoid instead of the softmax over all.
     ``weight_on="input"``: the weight multiplies what the expert READS (the result is the plain sum of
     expert(weight * h); needs ``n_identity`` 0); ``"output"``: what it returns.
-    ``shared``: the intermediate size of one more gated feed-forward of the same form that runs for every token and
+    ``shared``: the intermediate size of one more feed-forward of the same form that runs for every token and
     is added (names under ``shared``), or None.
+    ``gated=False``: an expert is down(act(up(h))) with ``activation`` silu, gelu_tanh or relu2 (no gate projection).
+    ``router_bias``: a bias per router output added to the logits (name ``router_bias``).  ``renormalise``: the chosen
+    weights are divided by their sum (with softmax scores: the softmax over the chosen logits alone).
+    ``shared_gate``: the shared expert's result is multiplied by sigmoid(w_sg . h), one number per token (name
+    ``shared_gate``, a tensor [1, width]).
 
     On the device throughout (no host reads): the router kernel, a sort of the (token, choice) pairs by expert,
     two products with one weight matrix per expert over the sorted pairs with the activation between them, and the
@@ -141,14 +146,19 @@ class RoutedMLP(Part):
     local names of its three projections, the router's and the correction's names."""
 
     DEFAULT_NAMES = {"expert": "e{e}.", "gate": "gate", "up": "up", "down": "down", "router": "router", "correction": "correction",
-                     "shared": "shared."}
+                     "shared": "shared.", "router_bias": "router.b", "shared_gate": "shared.sg"}
 
     graph_safe = True
 
     def __init__(self, dtype, device, width: int, intermediate: int, n_experts: int, top: int, scale: float = 1.0,
                  n_identity: int = 0, activation: str = "silu", correction: bool = True, names: "dict[str, str] | None" = None,
-                 scores: str = "softmax", weight_on: str = "output", shared: "int | None" = None):
+                 scores: str = "softmax", weight_on: str = "output", shared: "int | None" = None, gated: bool = True,
+                 router_bias: bool = False, renormalise: bool = False, shared_gate: bool = False):
         super().__init__(dtype, device)
+        self.gated, self.router_bias, self.renormalise = bool(gated), bool(router_bias), bool(renormalise)
+        self.shared_gate = bool(shared_gate) and bool(shared)
+        if self.router_bias and int(n_identity):
+            raise ValueError("a router bias and router outputs without weights do not go together")
         if scores not in ("softmax", "sigmoid") or weight_on not in ("output", "input"):
             raise ValueError(f"router scores {scores!r} / weight_on {weight_on!r}: 'softmax' or 'sigmoid', 'output' or 'input'")
         if weight_on == "input" and n_identity:
@@ -157,16 +167,24 @@ class RoutedMLP(Part):
         self.names = dict(self.DEFAULT_NAMES, **(names or {}))
         self.width, self.intermediate = int(width), int(intermediate)
         self.n_experts, self.n_identity, self.top, self.scale = int(n_experts), int(n_identity), int(top), float(scale)
-        if activation not in ops.ACTIVATIONS:
-            raise ops.UnsupportedSize(f"activation {activation!r}: implemented are {sorted(ops.ACTIVATIONS)}")
+        known = ops.ACTIVATIONS if self.gated else {k: v for k, v in ops.BIAS_ACTIVATIONS.items() if k not in (None, "tanh")}
+        if activation not in known:
+            raise ops.UnsupportedSize(f"activation {activation!r}: implemented are {sorted(known)}")
         if self.n_experts <= 0 or self.n_identity < 0 or not 0 < self.top <= self.n_experts + self.n_identity:
             raise ValueError(f"a routed feed-forward of {n_experts} + {n_identity} experts cannot choose {top}")
         self.activation, self.has_correction = activation, bool(correction)
-        self.w_gate_up = self.w_down = self.w_router = self.correction = self._ones = None
+        self.w_gate_up = self.w_down = self.w_router = self.correction = self._ones = self.b_router = self.w_shared_gate = None
         n = self.names
-        self.shared = make_part("ffn", PartSpec("gated_mlp", {
-            "width": self.width, "intermediate": int(shared), "activation": activation, "weight_suffix": "",
-            "names": {"gate": n["gate"], "up": n["up"], "down": n["down"]}}), dtype, device) if shared else None
+        if not shared:
+            self.shared = None
+        elif self.gated:
+            self.shared = make_part("ffn", PartSpec("gated_mlp", {
+                "width": self.width, "intermediate": int(shared), "activation": activation, "weight_suffix": "",
+                "names": {"gate": n["gate"], "up": n["up"], "down": n["down"]}}), dtype, device)
+        else:
+            self.shared = make_part("ffn", PartSpec("dense_mlp", {
+                "width": self.width, "intermediate": int(shared), "activation": activation,
+                "names": {"up": n["up"], "down": n["down"]}}), dtype, device)
 
     def children(self):
         return {self.names["shared"]: self.shared} if self.shared is not None else {}
@@ -175,30 +193,41 @@ class RoutedMLP(Part):
         n, t = self.names, {}
         for e in range(self.n_experts):
             pre = n["expert"].format(e=e)
-            t[pre + n["gate"]] = TensorSpec((self.intermediate, self.width))
+            if self.gated:
+                t[pre + n["gate"]] = TensorSpec((self.intermediate, self.width))
             t[pre + n["up"]] = TensorSpec((self.intermediate, self.width))
             t[pre + n["down"]] = TensorSpec((self.width, self.intermediate))
         outs = self.n_experts + self.n_identity
         t[n["router"]] = TensorSpec((outs, self.width), role="vector", init=("normal", 0.0, 0.05))
         if self.has_correction:
             t[n["correction"]] = TensorSpec((outs,), role="vector", init=("normal", 0.0, 0.02))
+        if self.router_bias:
+            t[n["router_bias"]] = TensorSpec((outs,), role="vector", init=("normal", 0.0, 0.05))
+        if self.shared_gate:
+            t[n["shared_gate"]] = TensorSpec((1, self.width), role="vector", init=("normal", 0.0, 0.05))
         return t
 
     def load(self, tensors):
         n = self.names
         pres = [n["expert"].format(e=e) for e in range(self.n_experts)]
-        self.w_gate_up = torch.stack([torch.cat([tensors[p + n["gate"]], tensors[p + n["up"]]], dim=0) for p in pres]).contiguous()
+        if self.gated:
+            self.w_gate_up = torch.stack([torch.cat([tensors[p + n["gate"]], tensors[p + n["up"]]], dim=0) for p in pres]).contiguous()
+        else:
+            self.w_gate_up = torch.stack([tensors[p + n["up"]] for p in pres]).contiguous()
         self.w_down = torch.stack([tensors[p + n["down"]] for p in pres]).contiguous()
         self.w_router = tensors[n["router"]]
         self.correction = tensors[n["correction"]] if self.has_correction else None
+        self.b_router = tensors[n["router_bias"]] if self.router_bias else None
+        self.w_shared_gate = tensors[n["shared_gate"]].reshape(-1).contiguous() if self.shared_gate else None
 
     def kernel_libraries(self):
-        return ["grouped", "parallel_block"]
+        return ["grouped", "parallel_block"] + ([] if self.gated else ["blockops"]) + (["seqmix"] if self.shared_gate else [])
 
     def forward(self, ctx, h):
         h = ops.materialize(h)
         T = h.shape[0]
-        idx, weight = ops.route(h, self.w_router, self.correction, self.top, self.scale, sigmoid=self.sigmoid)
+        idx, weight = ops.route(h, self.w_router, self.correction, self.top, self.scale, sigmoid=self.sigmoid,
+                                bias=self.b_router, renormalise=self.renormalise)
         offsets, place_of, src = ops.group_pairs(idx, self.n_experts)
         places = T * self.top
         x = h
@@ -208,11 +237,13 @@ class RoutedMLP(Part):
             weight = torch.ones_like(weight)
         with lib.section("experts_gate_up"):
             gu = ops.expert_linear(x, self.w_gate_up, offsets, src, places)
-        act = ops.act_mul(gu, self.activation)
+        act = ops.act_mul(gu, self.activation) if self.gated else ops.bias_act(gu, None, self.activation)
         with lib.section("experts_down"):
             y = ops.expert_linear(act, self.w_down, offsets, None, places, out_dtype=torch.float32)
         out = ops.combine_pairs(y, h, place_of, weight)
-        if self.shared is not None:
+        if self.shared is not None and self.shared_gate:
+            ops.token_gate_add(out, h, self.w_shared_gate, ops.materialize(self.shared.forward(ctx, h)))
+        elif self.shared is not None:
             ops.add_residual(out, ops.materialize(self.shared.forward(ctx, h)))
         # fp32 [T, width]: in bfloat16 it travels as the one part of a split product, which every norm adds unrounded
         return out if self.dtype == torch.float32 else ops.PartialSums(out.unsqueeze(0), self.dtype)

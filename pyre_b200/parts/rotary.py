@@ -21,7 +21,13 @@ class Rotary(PositionEncoding):
     ``scaling``: ``{"factor", "low", "high", "original"}`` stretches the slow frequencies for contexts beyond the
     ``original`` length: with the wavelength l = 2 pi / f, a frequency stays where l < original / high, becomes
     f / factor where l > original / low, and between the two is the blend (1 - s) f / factor + s f with
-    s = (original / l - low) / (high - low).  Computed once, in 64-bit."""
+    s = (original / l - low) / (high - low).  Computed once, in 64-bit.
+
+    ``scaling`` with the keys ``{"factor", "original", "fast", "slow"}`` is another rule: with d(t) = rotary_dim
+    ln(original / (2 pi t)) / (2 ln theta), the pair index whose wave turns t times within ``original`` positions,
+    lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rotary_dim - 1) and the ramp r_j = clamp((j - lo) /
+    max(hi - lo, 0.001), 0, 1), pair j gets the frequency f_j / factor * r_j + f_j (1 - r_j), and cos and sin are
+    multiplied by the amplitude 0.1 ln(factor) + 1."""
 
     graph_safe = True
 
@@ -45,7 +51,25 @@ class Rotary(PositionEncoding):
         else:
             inv = 1.0 / (self.theta ** (torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim))
         self.scaling = None
-        if scaling:
+        self.amplitude = 1.0
+        if scaling and ("fast" in scaling or "slow" in scaling):
+            try:
+                fac, orig, fast, slow = (float(scaling[k]) for k in ("factor", "original", "fast", "slow"))
+            except KeyError as e:
+                raise ValueError(f"rotary scaling needs factor, original, fast and slow; {e.args[0]!r} is missing") from None
+            if not (fac > 0 and orig > 0 and fast > 0 and slow > 0 and self.theta > 1):
+                raise ValueError(f"rotary scaling {scaling!r}: factor, original, fast and slow are positive")
+            self.scaling = ("turns", fac, orig, fast, slow)
+            f = self.theta ** (-torch.arange(0, self.rotary_dim, 2, dtype=torch.float64) / self.rotary_dim)
+
+            def turn_index(t):
+                return self.rotary_dim * math.log(orig / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))
+            lo = max(math.floor(turn_index(fast)), 0)
+            hi = min(math.ceil(turn_index(slow)), self.rotary_dim - 1)
+            ramp = ((torch.arange(self.rotary_dim // 2, dtype=torch.float64) - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            inv = (f / fac * ramp + f * (1.0 - ramp)).float()
+            self.amplitude = 0.1 * math.log(fac) + 1.0
+        elif scaling:
             try:
                 fac, lo, hi, orig = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
             except KeyError as e:
@@ -62,12 +86,15 @@ class Rotary(PositionEncoding):
         self._key = ("rotary", self.rotary_dim, self.theta, bool(exact_frequencies), self.scaling)
 
     def kernel_libraries(self):
-        return ["elementwise"]
+        return ["elementwise"] + (["seqmix"] if self.amplitude != 1.0 else [])
 
     def tables(self, ctx):
         tab = ctx.scratch.get(self._key)
         if tab is None:
             tab = ops.rope_table(ctx.positions, self.inv_freq)
+            if self.amplitude != 1.0:
+                for t in tab:
+                    ops.scale_cap(t, self.amplitude)
             ctx.scratch[self._key] = tab
         return tab
 

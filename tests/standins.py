@@ -177,7 +177,7 @@ def add_row_vector(x, v):
     return x
 
 
-def gated_norm(y, y_bias, gate, gate_bias, weight, eps, act_dtype, center=True):
+def gated_norm(y, y_bias, gate, gate_bias, weight, eps, act_dtype, center=True, out_bias=None):
     v = _partial_sums_or_tensor(y)
     if y_bias is not None:
         v = v + y_bias
@@ -185,7 +185,8 @@ def gated_norm(y, y_bias, gate, gate_bias, weight, eps, act_dtype, center=True):
         v = v * torch.sigmoid(gate.float() + (gate_bias if gate_bias is not None else 0.0))
     if center:
         v = v - v.mean(-1, keepdim=True)
-    return v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight
+    out = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * weight
+    return out if out_bias is None else out + out_bias
 
 
 def scale_to_places(h, place_of, weight, n_places):
@@ -284,7 +285,7 @@ def _branch(t):
     return t.float()
 
 
-def add_layernorm(x, delta, weight, eps, out_dtype, rows=None, update_x=True, act_dtype=None):
+def add_layernorm(x, delta, weight, eps, out_dtype, rows=None, update_x=True, act_dtype=None, bias=None):
     from pyre_b200.kernels import ops
     v = x
     if delta is not None:
@@ -296,7 +297,8 @@ def add_layernorm(x, delta, weight, eps, out_dtype, rows=None, update_x=True, ac
     if rows is not None:
         v = v[rows.long()]
     dev = v - v.mean(-1, keepdim=True)
-    return (dev * torch.rsqrt(dev.pow(2).mean(-1, keepdim=True) + eps) * weight).to(out_dtype)
+    out = dev * torch.rsqrt(dev.pow(2).mean(-1, keepdim=True) + eps) * weight
+    return (out if bias is None else out + bias).to(out_dtype)
 
 
 def act_mul(gate_up, kind):
@@ -368,11 +370,112 @@ def headwise_linear(x, w, out=None):
     return out
 
 
-def route(h, w, correction, top, scale, sigmoid=False):
-    s = torch.sigmoid(h.float() @ w.t()) if sigmoid else torch.softmax(h.float() @ w.t(), dim=-1)
+def route(h, w, correction, top, scale, sigmoid=False, bias=None, renormalise=False):
+    z = h.float() @ w.t()
+    if bias is not None:
+        z = z + bias
+    s = torch.sigmoid(z) if sigmoid else torch.softmax(z, dim=-1)
     choice = s if correction is None else s + correction
     idx = choice.topk(top, dim=-1).indices
-    return idx.to(torch.int32), s.gather(-1, idx) * scale
+    weight = s.gather(-1, idx) * scale
+    if renormalise:
+        weight = weight / weight.sum(-1, keepdim=True)
+    return idx.to(torch.int32), weight
+
+
+# --------------------------------------------------------------------------- short histories and recurrent states
+def scale_cap(x, scale=1.0, cap=0.0):
+    x.mul_(scale)
+    if cap > 0:
+        x.copy_(cap * torch.tanh(x / cap))
+    return x
+
+
+def short_conv(inp, col, n_ch, weight, bias, state_layer, state_off, slots, seq_of_token, cu_seqlens, silu=False, in_bias=None):
+    T = inp.shape[0]
+    taps = weight.shape[1]
+    u = inp[:, col:col + n_ch].float()
+    if in_bias is not None:
+        u = u + in_bias
+    out = torch.empty((T, n_ch), dtype=torch.float32)
+    cu = cu_seqlens.tolist()
+    for b in range(len(cu) - 1):
+        if cu[b + 1] == cu[b]:
+            continue
+        hist = state_layer[int(slots[b]), state_off:state_off + (taps - 1) * n_ch].view(taps - 1, n_ch)
+        seq = torch.cat([hist, u[cu[b]:cu[b + 1]]], dim=0)
+        n = cu[b + 1] - cu[b]
+        y = sum(seq[j:j + n] * weight[:, j] for j in range(taps))
+        out[cu[b]:cu[b + 1]] = y if bias is None else y + bias
+        hist.copy_(seq[n:].clone())
+    if silu:
+        out = torch.nn.functional.silu(out)
+    return out.to(inp.dtype)
+
+
+def ssm_scan(xbc, proj, dt_col, dt_bias, a_log, d_skip, state_layer, slots, cu_seqlens, n_heads, n_groups, p_dim, n_state):
+    T = xbc.shape[0]
+    H, G, P, N = n_heads, n_groups, p_dim, n_state
+    v = xbc.float()
+    x = v[:, :H * P].reshape(T, H, P)
+    B = v[:, H * P:H * P + G * N].reshape(T, G, N).repeat_interleave(H // G, dim=1)
+    C = v[:, H * P + G * N:].reshape(T, G, N).repeat_interleave(H // G, dim=1)
+    dt = torch.nn.functional.softplus(proj[:, dt_col:dt_col + H].float() + dt_bias, threshold=20.0)
+    dec = torch.exp(-torch.exp(a_log) * dt)
+    y = torch.empty((T, H, P), dtype=torch.float32)
+    cu = cu_seqlens.tolist()
+    for b in range(len(cu) - 1):
+        S = state_layer[int(slots[b]), :H * N * P].view(H, N, P)      # updated in place
+        for t in range(cu[b], cu[b + 1]):
+            S.mul_(dec[t][:, None, None]).add_((dt[t][:, None] * x[t])[:, None, :] * B[t][:, :, None])
+            y[t] = torch.einsum("hnp,hn->hp", S, C[t]) + d_skip[:, None] * x[t]
+    return y.reshape(T, H * P)
+
+
+def group_norm_gate(y, groups, weight, eps, proj, g_col, out_dtype, gate="silu", gate_first=False, post=1.0):
+    T, W = y.shape
+    act = torch.nn.functional.silu if gate == "silu" else torch.sigmoid
+    g = act(proj[:, g_col:g_col + W].float()) if proj is not None else None
+    v = y * g if (g is not None and gate_first) else y
+    v = v.reshape(T, groups, W // groups)
+    v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).reshape(T, W)
+    if weight is not None:
+        v = v * weight
+    v = v * post
+    if g is not None and not gate_first:
+        v = v * g
+    return v.to(out_dtype)
+
+
+def diff_combine(a, a_dim, lam, post, n_heads, n_kv_heads, v_dim, eps):
+    T = a.shape[0]
+    rep = n_heads // n_kv_heads
+    maps = a.float().reshape(T, n_kv_heads, 2, rep, a_dim)[..., :v_dim]
+    o = (maps[:, :, 0] - lam * maps[:, :, 1]).reshape(T, n_heads, v_dim)
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * post
+    return o.reshape(T, n_heads * v_dim).to(a.dtype)
+
+
+def rotate_heads(proj, col, n_heads, dim, cos, sin, rotary_dim, factor=1.0):
+    T = proj.shape[0]
+    v = proj[:, col:col + n_heads * dim].float().reshape(T, n_heads, dim)
+    if rotary_dim:
+        half = rotary_dim // 2
+        a, b, rest = v[..., :half], v[..., half:rotary_dim], v[..., rotary_dim:]
+        c, sn = cos[:, None, :], sin[:, None, :]
+        v = torch.cat([a * c - b * sn, b * c + a * sn, rest], dim=-1)
+    proj[:, col:col + n_heads * dim] = (v * factor).reshape(T, n_heads * dim).to(proj.dtype)
+    return proj
+
+
+def side_gate(pre, table, col, token_ids, err_flag=None):
+    e = table[token_ids.long()][:, col:col + pre.shape[1]].float()
+    return (torch.nn.functional.gelu(pre.float(), approximate="tanh") * e).to(pre.dtype)
+
+
+def token_gate_add(acc, h, w, y):
+    acc.add_(torch.sigmoid(h.float() @ w)[:, None] * y.float())
+    return acc
 
 
 def group_pairs(idx, n_experts):
@@ -425,7 +528,9 @@ def install(monkeypatch) -> None:
                          latent_attention=latent_attention, headwise_linear=headwise_linear, route=route, group_pairs=group_pairs,
                          expert_linear=expert_linear, combine_pairs=combine_pairs, head_gate=head_gate, bias_act=bias_act,
                          add_row_vector=add_row_vector, gated_norm=gated_norm, scale_to_places=scale_to_places,
-                         token_shift_mix=token_shift_mix, wkv_scan=wkv_scan).items():
+                         token_shift_mix=token_shift_mix, wkv_scan=wkv_scan, scale_cap=scale_cap, short_conv=short_conv,
+                         ssm_scan=ssm_scan, group_norm_gate=group_norm_gate, diff_combine=diff_combine, rotate_heads=rotate_heads,
+                         side_gate=side_gate, token_gate_add=token_gate_add).items():
         monkeypatch.setattr(ops, name, fn)
     monkeypatch.setattr(ops, "device_error_flag", lambda device: flag)
     monkeypatch.setattr(ops, "check_device_errors", lambda device="cpu": None)
