@@ -30,6 +30,13 @@ def build_nipudra(cfg: NipudraConfig) -> ModelSpec:
     def norm():
         return PartSpec("layer_norm", {"width": cfg.width, "eps": cfg.norm_eps, "tensor_name": "", "bias_name": ".b"})
 
+    # a cache layer keeps what the widest window among its writer and its readers shows (None: every key)
+    keep: dict = {}
+    for i, L in enumerate(cfg.layers):
+        if L.kind == "attention":
+            src = L.kv_from if L.kv_from >= 0 else i
+            seen = keep.get(src, 0)
+            keep[src] = None if (seen is None or not L.window) else max(seen, L.window)
     blocks, schedule = [], []
     for i, L in enumerate(cfg.layers):
         call = LayerCall(i)
@@ -43,7 +50,8 @@ def build_nipudra(cfg: NipudraConfig) -> ModelSpec:
             mixer = PartSpec("differential_attention", {
                 "width": cfg.width, "n_heads": L.heads, "n_kv_heads": L.kv_heads, "head_dim": L.dim, "v_head_dim": L.vdim,
                 "diff": L.diff, "eps": cfg.norm_eps, "scale": L.scale, "window": L.window or None, "position": position,
-                "conv_taps": L.conv, "qkv_bias": True, "o_bias": True, "own_kv": not shares})
+                "conv_taps": L.conv, "qkv_bias": True, "o_bias": True, "own_kv": not shares,
+                "cache_window": keep[L.kv_from if shares else i]})
             call = LayerCall(i, cache=("layer", L.kv_from if shares else i), write=not shares)
         elif L.kind == "mamba2":
             mixer = PartSpec("mamba2", {"width": cfg.width, "n_heads": L.heads, "p_dim": L.vdim, "n_state": L.state,

@@ -26,7 +26,9 @@ class DifferentialAttention(Part):
     over time on every channel of q, k and v, right after the projection (names ``<projection>.conv``); the last
     ``conv_taps - 1`` projected rows of a request live in its state slot.  Then the position encoding (a sub-part)
     turns each map's queries and keys and keys and values go to the cache.  ``own_kv=False``: the mixer projects
-    queries only and reads the cache layer another schedule entry writes.
+    queries only and reads the cache layer another schedule entry writes.  ``cache_window``: how far back the cache
+    layer must keep keys (default: ``window``); a layer whose cache is read by layers with other windows names the
+    widest of them (None: everything), and so do its readers, so that all of them ask the same of the cache manager.
 
     For the package's attention kernels a map is a head of its own: 2 n_heads query heads over 2 n_kv_heads key/value
     heads, the query maps ordered (g, m, r) so that the kernels' grouping sends map m of head g * rep + r to key head
@@ -40,7 +42,7 @@ class DifferentialAttention(Part):
     def __init__(self, dtype, device, width: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int, diff: float,
                  eps: float, scale: "float | None" = None, window: "int | None" = None, position: "PartSpec | None" = None,
                  conv_taps: int = 0, qkv_bias: bool = True, o_bias: bool = True, own_kv: bool = True,
-                 names: "dict[str, str] | None" = None):
+                 names: "dict[str, str] | None" = None, cache_window: "int | None | str" = "window"):
         super().__init__(dtype, device)
         self.names = dict(self.DEFAULT_NAMES, **(names or {}))
         self.width, self.n_heads, self.n_kv_heads = int(width), int(n_heads), int(n_kv_heads)
@@ -53,6 +55,9 @@ class DifferentialAttention(Part):
         self.diff, self.eps = float(diff), float(eps)
         self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
         self.window, self.conv_taps = window, int(conv_taps)
+        self.cache_window = window if cache_window == "window" else cache_window
+        if self.cache_window is not None and (window is None or self.cache_window < window):
+            raise ValueError("the cache must keep at least the keys that the window shows")
         if self.conv_taps == 1 or self.conv_taps < 0:
             raise ops.UnsupportedSize("a convolution over time has at least two taps (0: none)")
         self.qkv_bias, self.o_bias, self.own_kv = bool(qkv_bias), bool(o_bias), bool(own_kv)
@@ -121,7 +126,7 @@ class DifferentialAttention(Part):
             (["gemm_f32"] if self.dtype == torch.float32 else ["gemm_tc"])
 
     def cache_spec(self):
-        return PagedKVSpec(2 * self.n_kv_heads, self.row_dim, self.window)
+        return PagedKVSpec(2 * self.n_kv_heads, self.row_dim, self.cache_window)
 
     def state_spec(self):
         return StateSpec(((self.conv_taps - 1) * self.n_ch,), torch.float32) if self.conv_taps > 1 else None

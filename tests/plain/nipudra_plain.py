@@ -106,13 +106,23 @@ def windowed_softmax(scores, window):
     return torch.softmax(scores.masked_fill(~seen, float("-inf")), dim=-1)
 
 
+def projected(h, w, name, lowp):
+    """A biased projection, then its short convolution when the layer has one (``<name>.conv``)."""
+    y = matmul(h, w[name], lowp, w[name + ".b"])
+    return _r(short_convolution(y, w[name + ".conv"]), lowp) if name + ".conv" in w else y
+
+
+def map_frequencies(mixer):
+    rot = mixer.get("rot") or {}
+    return rotary_frequencies(rot["base"], rot["dims"], rot.get("scaling")) if rot.get("dims") else ([], 1.0)
+
+
 def attention_keys_values(h, w, prefix, mixer, positions, lowp=False):
     """What a layer caches: keys after convolution and rotation [T, G, 2, dim], values after convolution [T, G, vdim]."""
     G, dim, vdim = mixer["kv_heads"], mixer["dim"], mixer["vdim"]
     T = h.shape[0]
-    k = _r(short_convolution(matmul(h, w[prefix + "k"], lowp, w[prefix + "k.b"]), w[prefix + "k.conv"]), lowp)
-    v = _r(short_convolution(matmul(h, w[prefix + "v"], lowp, w[prefix + "v.b"]), w[prefix + "v.conv"]), lowp)
-    freqs, amp = rotary_frequencies(mixer["rot"]["base"], mixer["rot"]["dims"], mixer["rot"].get("scaling"))
+    k, v = projected(h, w, prefix + "k", lowp), projected(h, w, prefix + "v", lowp)
+    freqs, amp = map_frequencies(mixer)
     k = rotate_halves(k.reshape(T, 2 * G, dim), positions, freqs, amp).reshape(T, G, 2, dim)
     return _r(k, lowp), v.reshape(T, G, vdim)
 
@@ -123,8 +133,8 @@ def differential_attention(h, w, prefix, mixer, eps, keys, values, lowp=False):
     H, G, dim, vdim = mixer["heads"], mixer["kv_heads"], mixer["dim"], mixer["vdim"]
     T = h.shape[0]
     positions = torch.arange(T)
-    q = _r(short_convolution(matmul(h, w[prefix + "q"], lowp, w[prefix + "q.b"]), w[prefix + "q.conv"]), lowp)
-    freqs, amp = rotary_frequencies(mixer["rot"]["base"], mixer["rot"]["dims"], mixer["rot"].get("scaling"))
+    q = projected(h, w, prefix + "q", lowp)
+    freqs, amp = map_frequencies(mixer)
     q = _r(rotate_halves(q.reshape(T, 2 * H, dim), positions, freqs, amp), lowp).reshape(T, H, 2, dim)
     f = lambda name: w[prefix + name].to(F64)
     lam = math.exp(float((f("lq1") * f("lk1")).sum())) - math.exp(float((f("lq2") * f("lk2")).sum())) + mixer["diff"]
@@ -133,7 +143,7 @@ def differential_attention(h, w, prefix, mixer, eps, keys, values, lowp=False):
         g = n // (H // G)
         maps = []
         for m in range(2):
-            p = windowed_softmax(q[:, n, m] @ keys[:, g, m].T * mixer["scale"], mixer["mask"]["size"])
+            p = windowed_softmax(q[:, n, m] @ keys[:, g, m].T * mixer["scale"], (mixer.get("mask") or {}).get("size") or T)
             maps.append(_r(p, lowp) @ values[:, g])
         o = maps[0] - lam * maps[1]
         heads.append(unit_rms(o, eps) * (1.0 - mixer["diff"]))
@@ -145,7 +155,7 @@ def retention(h, w, prefix, mixer, eps, lowp=False):
     H, dim, vdim = mixer["heads"], mixer["dim"], mixer["vdim"]
     T = h.shape[0]
     positions = torch.arange(T)
-    freqs, _ = rotary_frequencies(mixer["rot"]["base"], mixer["rot"]["dims"])
+    freqs, _ = map_frequencies(mixer)
     q = _r(rotate_halves(matmul(h, w[prefix + "q"], lowp).reshape(T, H, dim), positions, freqs), lowp)
     k = _r(rotate_halves(matmul(h, w[prefix + "k"], lowp).reshape(T, H, dim), positions, freqs) * dim ** -0.5, lowp)
     v = matmul(h, w[prefix + "v"], lowp).reshape(T, H, vdim)
@@ -237,7 +247,7 @@ def forward(config, w, tokens, lowp=False, keep_layers=False, margins=None):
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     T = tokens.shape[0]
     positions = torch.arange(T)
-    x = w["embed"].to(F64)[tokens] * config["embedding"]["scale"]
+    x = w["embed"].to(F64)[tokens] * (config.get("embedding") or {}).get("scale", 1.0)
     side = config.get("token_side")
     cached, streams = {}, []
     for i, L in enumerate(config["layers"]):
@@ -264,7 +274,7 @@ def forward(config, w, tokens, lowp=False, keep_layers=False, margins=None):
             x = token_side_input(x, tokens, w, p + "side.", i, side["dim"], eps, lowp)
         streams.append(x.clone())
     h = layer_norm(x, w["final.norm"], w["final.norm.b"], eps)
-    logits = matmul(h, w["embed"], lowp) * config["logit_scale"]
+    logits = matmul(h, w["embed"], lowp) * config.get("logit_scale", 1.0)
     cap = config.get("logit_softcap")
     if cap:
         logits = cap * torch.tanh(logits / cap)
