@@ -963,6 +963,127 @@ def run_tekarax(args) -> dict:
     return out
 
 
+def run_nipudra(args) -> dict:
+    """``--workload nipudra``: the Nipudra design (random weights) at two sets of layer sizes, three layers (retention,
+    differential attention over a window with short convolutions, a state-space recurrence; each with routed experts
+    and a shared one, and a per-layer input from a side table), beside the package's closest layers at equal sizes:
+    two Tekarax layers (its recurrent layer and its softmax-attention layer, each with routed experts and a shared
+    one between two layer norms per sublayer) and Modovik's constant-decay recurrent layer with a dense feed-forward.
+    A 2,048-token prompt step and decode steps at batch 8 and 64 with 2,048 tokens of context, device-timed, and per
+    kernel class the device time of one such step with the fraction of the measured peak."""
+    import numpy as np
+
+    from pyre_b200.config import config_from_dict
+
+    peaks = load_peaks()
+    V = 32768
+    sizes = {
+        # width; heads / key-value heads / map size of the attention; retention heads of 128; state-space heads of 64
+        # with a state of 128 rows in 8 groups; window; experts, chosen, their size, the shared one's; side table
+        "2k": dict(H=2048, nh=8, nkv=2, hd=128, win=1024, E=32, top=4, ff=1024, sh=2048, side=256),
+        "3.5k": dict(H=3584, nh=14, nkv=2, hd=128, win=4096, E=64, top=6, ff=1408, sh=2816, side=256),
+    }
+    T, ctx_len = PROMPT_LEN, 2048
+    rng = np.random.default_rng(0)
+    out = {"workload": "nipudra", "peaks": peaks, "prompt": T, "decode_context": ctx_len, "sizes": {}}
+    for tag, z in sizes.items():
+        H, nh, nkv, hd, win, E, top, ff, sh, side = (z[k] for k in ("H", "nh", "nkv", "hd", "win", "E", "top", "ff", "sh", "side"))
+        rh, rd = H // 128, 128                                 # retention: heads x size = width
+        mh, P, N, G, taps = 2 * H // 64, 64, 128, 8, 4         # state space: inner = 2 x width
+        inner, conv_ch = mh * P, mh * P + 2 * G * N
+        moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top}, "shared": {"ff": sh}}
+        rot = {"dims": 64, "base": 1e6, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}
+        raw_n = {"architecture": "Nipudra", "vocab": V, "width": H, "norm": {"eps": 1e-6}, "embedding": {"scale": H ** 0.5},
+                 "logit_scale": 0.25, "logit_softcap": 30.0, "token_side": {"dim": side}, "layers": [
+            {"type": "retention", "mixer": {"heads": rh, "dim": rd, "vdim": rd, "decay": [1.0 - 2.0 ** (-5 - 3 * i / rh) for i in range(rh)],
+                                            "rot": {"dims": 64, "base": 1e6}}, "mlp": moe},
+            {"type": "attention", "mixer": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "diff": 0.3, "conv": taps,
+                                            "mask": {"size": win}, "rot": rot}, "mlp": moe},
+            {"type": "mamba2", "mixer": {"heads": mh, "vdim": P, "state": N, "groups": G, "conv": taps, "norm_groups": G}, "mlp": moe}]}
+        wh, wd, wr = H // 64, 64, 64
+        trot = {"dims": 64, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+        raw_t = {"architecture": "Tekarax", "vocab": V, "width": H, "norm": {"eps": 1e-6}, "layers": [
+            {"type": "wkv", "mixer": {"heads": wh, "dim": wd, "decay_rank": wr}, "mlp": moe},
+            {"type": "attention", "mixer": {"heads": 2 * nh, "kv_heads": 2 * nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "rot": trot}, "mlp": moe}]}
+        raw_m = {"architecture": "Modovik", "vocab": V, "width": H, "norm": {"eps": 1e-6}, "layers": [
+            {"type": "lightning", "mixer": {"heads": rh, "dim": rd, "vdim": rd, "decay": [1.0 - 2.0 ** (-5 - 3 * i / rh) for i in range(rh)]},
+             "mlp": {"kind": "dense", "ff": 4 * H}}]}
+        q_maps, k_maps = 2 * nh * hd, 2 * nkv * hd             # the attention's maps: each a head of the kernels
+
+        def attention_pairs(Tn, B, before, window=None):
+            first = np.arange(before, before + Tn // B)
+            return B * float((np.minimum(first + 1, window) if window else first + 1).sum())
+
+        def routed(Tn, n, gated):
+            pairs, up = Tn * top, 2 if gated else 1
+            used = min(E, pairs)
+            w = {"experts_gate_up": {"bytes": n * (used * up * ff * H * 2 + pairs * (H + up * ff) * 2), "flops": 2.0 * n * up * pairs * H * ff},
+                 "experts_down": {"bytes": n * (used * H * ff * 2 + pairs * (ff * 2 + H * 4)), "flops": 2.0 * n * pairs * H * ff},
+                 "router": {"bytes": n * (E * H * 4 + Tn * H * 2 + pairs * H * (4 + 2) + Tn * H * 4), "flops": 2.0 * n * Tn * H * E}}
+            if gated:
+                w["gate_up"] = {"bytes": n * (2 * sh * H * 2 + Tn * (H + 2 * sh) * 2), "flops": 4.0 * n * Tn * H * sh}
+            else:
+                w["up"] = {"bytes": n * (sh * H * 2 + Tn * (H + sh) * 2), "flops": 2.0 * n * Tn * H * sh}
+            w["down"] = {"bytes": n * (H * sh * 2 + Tn * (sh + H) * 2), "flops": 2.0 * n * Tn * H * sh}
+            return w
+
+        def tail(Tn, B):
+            return {"head": {"bytes": V * H * 2 + B * (H * 2 + V * 4), "flops": 2.0 * B * H * V}, "embed": {"bytes": Tn * H * (2 + 4), "flops": 0}}
+
+        def work_nipudra(Tn, B, before):
+            proj = 4 * rh * rd + (q_maps + k_maps + k_maps) + (2 * inner + 2 * G * N + mh)      # q k v g | maps, values per map | z x B C dt
+            cached = B * min(before + Tn // B, win + Tn // B)
+            return {
+                "qkv": {"bytes": proj * H * 2 + Tn * (3 * H + proj) * 2, "flops": 2.0 * Tn * H * proj},
+                "short_conv": {"bytes": Tn * (q_maps + 2 * k_maps + conv_ch) * (2 + 2) + B * (taps - 1) * (q_maps + 2 * k_maps + conv_ch) * 8, "flops": 0},
+                "linear_attention": {"bytes": Tn * 3 * rh * rd * 2 + Tn * rh * rd * 4 + B * 2 * rh * rd * rd * 4, "flops": 4.0 * Tn * rh * rd * rd},
+                "recurrence": {"bytes": Tn * (conv_ch * 2 + inner * 4) + B * 2 * mh * N * P * 4, "flops": 6.0 * Tn * mh * N * P},
+                "attention": {"bytes": cached * 2 * k_maps * 2 + 2 * Tn * q_maps * 2, "flops": 4.0 * 2 * nh * hd * attention_pairs(Tn, B, before, win)},
+                "o": {"bytes": (rh * rd + nh * hd + inner) * H * 2 + Tn * (rh * rd + nh * hd + inner + 3 * H) * 2,
+                      "flops": 2.0 * Tn * H * (rh * rd + nh * hd + inner)},
+                "side": {"bytes": 3 * (2 * side * H * 2 + Tn * (2 * H + 3 * side) * 2), "flops": 3 * 4.0 * Tn * H * side},
+                "activation": {"bytes": 3 * Tn * top * 2 * ff * 2 + 3 * Tn * 2 * sh * 2 + Tn * H * 2 * 2, "flops": 0},
+                "norm": {"bytes": Tn * H * (2 + 2 + 4 + 4), "flops": 0, "per_launch": True},
+                "gate": {"bytes": Tn * inner * (4 + 2 + 2) // 2, "flops": 0, "per_launch": True},
+                "rotary+write": {"bytes": Tn * (q_maps + 2 * k_maps) * 2 * 2, "flops": 0, "per_launch": True},
+                **routed(Tn, 3, False), **tail(Tn, B)}
+
+        def work_tekarax(Tn, B, before):
+            whd = wh * wd
+            proj = 4 * whd + (q_maps + 2 * k_maps + 2 * nh)
+            return {
+                "qkv": {"bytes": proj * H * 2 + Tn * (5 * H + proj) * 2, "flops": 2.0 * Tn * H * proj},
+                "decay": {"bytes": (wr * H + whd * wr) * 2 + Tn * (H + 2 * wr) * 2 + Tn * whd * 4, "flops": 2.0 * Tn * wr * (H + whd)},
+                "recurrence": {"bytes": Tn * (H * 2 * 6 + whd * (2 * 5 + 4)) + B * (2 * wh * wd * wd + 2 * H) * 4, "flops": 6.0 * Tn * wh * wd * wd},
+                "attention": {"bytes": B * (before + Tn // B) * 2 * k_maps * 2 + 2 * Tn * q_maps * 2, "flops": 4.0 * 2 * nh * hd * attention_pairs(Tn, B, before)},
+                "o": {"bytes": (whd + q_maps) * H * 2 + Tn * (whd + q_maps + 2 * H) * 2, "flops": 2.0 * Tn * H * (whd + q_maps)},
+                "residual_gate": {"bytes": 4 * (H * H * 2 + Tn * 2 * H * 2), "flops": 2.0 * 4 * Tn * H * H},
+                "activation": {"bytes": 2 * Tn * top * 3 * ff * 2 + 2 * Tn * 3 * sh * 2 + Tn * wr * 4, "flops": 0},
+                "norm": {"bytes": Tn * H * (2 + 2 + 4 + 4), "flops": 0, "per_launch": True},
+                "gate": {"bytes": Tn * q_maps * (2 + 2), "flops": 0, "per_launch": True},
+                "rotary+write": {"bytes": Tn * (q_maps + 2 * k_maps) * 2 * 2, "flops": 0, "per_launch": True},
+                **routed(Tn, 2, True), **tail(Tn, B)}
+
+        def work_modovik(Tn, B, before):
+            I = 4 * H
+            return {
+                "qkv": {"bytes": 4 * rh * rd * H * 2 + Tn * (H + 4 * rh * rd) * 2, "flops": 2.0 * Tn * H * 4 * rh * rd},
+                "linear_attention": {"bytes": Tn * 3 * rh * rd * 2 + Tn * rh * rd * 4 + B * 2 * rh * rd * rd * 4, "flops": 4.0 * Tn * rh * rd * rd},
+                "o": {"bytes": rh * rd * H * 2 + Tn * (rh * rd + H) * 2, "flops": 2.0 * Tn * H * rh * rd},
+                "up": {"bytes": I * H * 2 + Tn * (H + I) * 2, "flops": 2.0 * Tn * H * I},
+                "down": {"bytes": H * I * 2 + Tn * (I + H) * 2, "flops": 2.0 * Tn * H * I},
+                "activation": {"bytes": Tn * I * 4, "flops": 0},
+                "norm": {"bytes": Tn * H * (2 + 4 + 4 + 2), "flops": 0, "per_launch": True},
+                "gate": {"bytes": Tn * rh * rd * (4 + 2 + 2), "flops": 0, "per_launch": True},
+                **tail(Tn, B)}
+
+        block = {"sizes": dict(z, retention_heads=rh, state_space_heads=mh, state=N, groups=G), "models": {}}
+        for name, raw, work in (("nipudra", raw_n, work_nipudra), ("tekarax", raw_t, work_tekarax), ("modovik", raw_m, work_modovik)):
+            block["models"][name] = dict(layers=len(raw["layers"]), **_measure_design(config_from_dict(raw), work, args, peaks, V, T, ctx_len, rng))
+        out["sizes"][tag] = block
+    return out
+
+
 def run_sweep(args) -> dict:
     """Decode throughput over a grid of batch sizes and context lengths and prefill throughput over
     several portion lengths on the 7B shape, each with its fraction of the roofline (device-timed,
@@ -1086,11 +1207,11 @@ def main() -> int:
                     help="leave out the points at longer contexts and at the 14B and 32B shapes")
     ap.add_argument("--no-per-kernel", action="store_true",
                     help="leave out the `kernels` block (device time, bytes or flops and fraction of the peak per kernel class)")
-    ap.add_argument("--workload", choices=["serve14b", "mixed32b", "sweep", "modovik", "pivinex", "tekarax"], default=None,
+    ap.add_argument("--workload", choices=["serve14b", "mixed32b", "sweep", "modovik", "pivinex", "tekarax", "nipudra"], default=None,
                     help="run one of the two other baseline workloads, a sweep over batch sizes, context lengths and "
                          "portion lengths on the 7B shape, the Modovik or the Pivinex design beside the Qwen2.5 decoder at "
-                         "equal layer sizes, or the Tekarax design beside the closest layers of those two, instead (prints "
-                         "its own JSON line)")
+                         "equal layer sizes, the Tekarax design beside the closest layers of those two, or the Nipudra design beside the closest "
+                         "layers of Tekarax and Modovik, instead (prints its own JSON line)")
     ap.add_argument("--cache-fraction", type=float, default=1.0,
                     help="serve14b: cache capacity as a fraction of what all requests need at once (< 1 forces preemption)")
     args = ap.parse_args()
@@ -1099,7 +1220,7 @@ def main() -> int:
         return 2
     if args.workload:
         result = run_sweep(args) if args.workload == "sweep" else run_modovik(args) if args.workload == "modovik" else \
-            run_pivinex(args) if args.workload == "pivinex" else run_tekarax(args) if args.workload == "tekarax" else run_workload(args)
+            run_pivinex(args) if args.workload == "pivinex" else run_tekarax(args) if args.workload == "tekarax" else run_nipudra(args) if args.workload == "nipudra" else run_workload(args)
         result["env"] = environment()
         print(json.dumps(result))
         return 0

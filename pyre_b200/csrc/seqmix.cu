@@ -57,12 +57,11 @@ __global__ void short_conv_kernel(const T* in, long long row_stride, int col, co
                                   int silu) {
     pdl_trigger();
     pdl_wait();
-    const size_t total = (size_t)n_tokens * n_ch, stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int t = (int)(i / n_ch), c = (int)(i - (size_t)t * n_ch);
-        const int b = seq_of_token[t];
-        const int first = cu_seqlens[b];
-        const float* hist = state + (size_t)slots[b] * slot_stride + state_off;
+    const int t = blockIdx.x;                                  // a token per block row, the channels across threads and blockIdx.y
+    const int b = seq_of_token[t];
+    const int first = cu_seqlens[b];
+    const float* hist = state + (size_t)slots[b] * slot_stride + state_off;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n_ch; c += gridDim.y * blockDim.x) {
         float acc = bias ? bias[c] : 0.f;
         const float ib = in_bias ? in_bias[c] : 0.f;
         for (int j = 0; j < taps; ++j) {
@@ -71,7 +70,63 @@ __global__ void short_conv_kernel(const T* in, long long row_stride, int col, co
                                        : hist[(size_t)(taps - 1 + local) * n_ch + c];
             acc = fmaf(w[(size_t)c * taps + j], u, acc);
         }
-        out[i] = from_f32<T>(silu ? sm_silu(acc) : acc);
+        out[(size_t)t * n_ch + c] = from_f32<T>(silu ? sm_silu(acc) : acc);
+    }
+}
+
+// The same for up to CONV_MAX_TAPS taps, a tile of CONV_TILE consecutive tokens per block: a thread walks its channel
+// through the tile with the last inputs in registers, so every input and every tap is read once.  The window is filled
+// anew where the tile or an entry begins (from the tokens before, or from the history).  Same sum, same order.
+constexpr int CONV_MAX_TAPS = 8;
+constexpr int CONV_TILE = 8;
+
+template <typename T>
+__global__ void short_conv_tiled_kernel(const T* in, long long row_stride, int col, const float* in_bias, const float* w,
+                                        const float* bias, const float* state, long long slot_stride, long long state_off,
+                                        const int* slots, const int* seq_of_token, const int* cu_seqlens, T* out, int n_tokens,
+                                        int n_ch, int taps, int silu) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= n_ch) return;
+    const int t0 = blockIdx.x * CONV_TILE, t1 = min(t0 + CONV_TILE, n_tokens);
+    float wt[CONV_MAX_TAPS], u[CONV_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+        wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+        u[j] = 0.f;
+    }
+    const float b0 = bias ? bias[c] : 0.f, ib = in_bias ? in_bias[c] : 0.f;
+    int entry = -1;
+    for (int t = t0; t < t1; ++t) {
+        const int b = seq_of_token[t];
+        if (b != entry) {                                      // the window's first taps - 1 inputs: tokens before, or the history
+            entry = b;
+            const int first = cu_seqlens[b];
+            const float* hist = state + (size_t)slots[b] * slot_stride + state_off;
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {
+                if (j < taps - 1) {
+                    const int local = t - first - (taps - 1) + j;
+                    u[j] = local >= 0 ? __fadd_rn(to_f32<T>(in[(size_t)(first + local) * row_stride + col + c]), ib)
+                                      : hist[(size_t)(taps - 1 + local) * n_ch + c];
+                }
+            }
+        }
+        const float now = __fadd_rn(to_f32<T>(in[(size_t)t * row_stride + col + c]), ib);
+        float acc = b0;
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+            if (j < taps) {
+                const float v = j == taps - 1 ? now : u[j];
+                acc = fmaf(wt[j], v, acc);
+            }
+        }
+        out[(size_t)t * n_ch + c] = from_f32<T>(silu ? sm_silu(acc) : acc);
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) {          // the window moves on by one input
+            if (j < taps - 1) u[j] = j == taps - 2 ? now : u[j + 1];
+        }
     }
 }
 
@@ -105,11 +160,18 @@ PYRE_API int pyre_short_conv(const void* in, long long row_stride, int col, cons
                              cudaStream_t stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
     if (n_ch <= 0 || taps < 1 || col < 0 || !w || !state || !slots || !seq_of_token || !cu_seqlens) return PYRE_ERR_BAD_ARG;
-    const long long total = (long long)n_tokens * n_ch;
-    const int blocks = (int)min((long long)pyre_sm_count() * 16, ceil_div_ll(total, 256));
+    const dim3 blocks(n_tokens, min(ceil_div(n_ch, 256), 64));
     const int sblocks = (int)min((long long)pyre_sm_count() * 4, ceil_div_ll((long long)n_seqs * n_ch, 128));
+    // prompt portions walk tiles of tokens; steps of single tokens (every token another entry) keep a thread per element
+    const bool tiled = taps <= CONV_MAX_TAPS && n_tokens >= 8 * n_seqs;
+    const dim3 tiles(ceil_div(n_tokens, CONV_TILE), ceil_div(n_ch, 128));
     if (dtype == PYRE_BF16) {
-        pyre_launch(short_conv_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)in, row_stride, col, in_bias, w,
+        if (tiled)
+            pyre_launch(short_conv_tiled_kernel<__nv_bfloat16>, tiles, dim3(128), 0, stream, (const __nv_bfloat16*)in, row_stride, col,
+                        in_bias, w, bias, (const float*)state, slot_stride, state_off, slots, seq_of_token, cu_seqlens,
+                        (__nv_bfloat16*)out, n_tokens, n_ch, taps, silu);
+        else
+        pyre_launch(short_conv_kernel<__nv_bfloat16>, blocks, dim3(256), 0, stream, (const __nv_bfloat16*)in, row_stride, col, in_bias, w,
                     bias, (const float*)state, slot_stride, state_off, slots, seq_of_token, cu_seqlens, (__nv_bfloat16*)out, n_tokens,
                     n_ch, taps, silu);
         PYRE_LAUNCH_CHECK();
@@ -117,7 +179,12 @@ PYRE_API int pyre_short_conv(const void* in, long long row_stride, int col, cons
             pyre_launch(short_conv_state_kernel<__nv_bfloat16>, dim3(sblocks), dim3(128), 0, stream, (const __nv_bfloat16*)in, row_stride,
                         col, in_bias, state, slot_stride, state_off, slots, cu_seqlens, n_seqs, n_ch, taps);
     } else if (dtype == PYRE_F32) {
-        pyre_launch(short_conv_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)in, row_stride, col, in_bias, w, bias,
+        if (tiled)
+            pyre_launch(short_conv_tiled_kernel<float>, tiles, dim3(128), 0, stream, (const float*)in, row_stride, col, in_bias, w, bias,
+                        (const float*)state, slot_stride, state_off, slots, seq_of_token, cu_seqlens, (float*)out, n_tokens, n_ch,
+                        taps, silu);
+        else
+        pyre_launch(short_conv_kernel<float>, blocks, dim3(256), 0, stream, (const float*)in, row_stride, col, in_bias, w, bias,
                     (const float*)state, slot_stride, state_off, slots, seq_of_token, cu_seqlens, (float*)out, n_tokens, n_ch, taps,
                     silu);
         PYRE_LAUNCH_CHECK();
@@ -135,132 +202,203 @@ PYRE_API int pyre_short_conv(const void* in, long long row_stride, int col, cons
 //   dt  = softplus(raw + dt_bias[h])                 decay = exp(-exp(A_log[h]) * dt)
 //   S_t = decay * S_(t-1) + dt * B_t x_t^T           S [N, P] fp32, in the request's state slot
 //   y_t = S_t^T C_t + D[h] x_t                       fp32 [T, H P]
-// A column of S never meets another column, so the grid is (tiles of 32 columns, heads, entries).  A CTA of four warps
-// keeps its [N, 32] tile in registers for the whole entry: a warp owns eight columns, its lanes split the rows four
-// ways (row n belongs to lane group n mod 4), and a column's four partial sums meet in two shuffles.  Tokens are
-// staged through shared memory sixteen at a time (B, C, x, dt and the decay, evaluated while staging); a token's
-// arithmetic does not depend on where a chunk begins, so results are bit-identical under cutting and batching.
+// A column of S never meets another column, so the grid is (tiles of 32 columns, heads, entries).  A CTA keeps its
+// [N, 32] tile in registers for the whole entry: a warp owns 32 / RG columns, its lanes split the rows RG ways (lane
+// group r has the NR rows from r * NR, which it reads from shared memory as 16-byte vectors; rows beyond N are padding
+// whose B is zero), and a column's partial sums meet in log2(RG) shuffles.  RG = 4 (four warps, eight
+// columns each): a row segment of a warp's state is a whole 32-byte sector, for steps of single tokens, where reading
+// and writing the state is the work.  RG = 16 (sixteen warps, two columns each): a quarter of the rows per thread and
+// four times the warps, for prompt portions, where the token loop's latency is the work.  Tokens are staged through
+// shared memory sixteen at a time (B, C, x, dt and the decay, evaluated while staging); a token's arithmetic does not
+// depend on where a chunk begins, so with one RG results are bit-identical under cutting and batching.
 // ---------------------------------------------------------------------------
 constexpr int SSM_COLS = 32;      // columns of a CTA
 constexpr int SSM_STAGE = 16;     // tokens staged at a time
 
-template <typename T, int NR>     // NR: rows per thread, N <= 4 NR
-__global__ void __launch_bounds__(128)
+template <typename T, int NR, int RG>     // NR: rows per thread, N <= RG * NR =: NP, the rows with padding
+__global__ void __launch_bounds__(SSM_COLS * RG)
 ssm_scan_kernel(const T* xbc, long long xbc_stride, const T* proj, long long proj_stride, int dt_col, const float* dt_bias,
                 const float* A_log, const float* D, float* state, long long slot_stride, const int* slots,
                 const int* cu_seqlens, float* y, int H, int G, int P, int N) {
-    extern __shared__ float ssm_smem[];   // [STAGE][2 N] B | C, then [STAGE][COLS] x, then [STAGE] dt, [STAGE] decay
+    extern __shared__ __align__(16) float ssm_smem[];   // [STAGE][2 NP] B | C (zeros beyond N), [STAGE][COLS] x, [STAGE] dt, [STAGE] decay
     pdl_trigger();
     pdl_wait();
+    constexpr int NP = NR * RG, THREADS = SSM_COLS * RG, CPW = 32 / RG;      // CPW: columns of a warp
+    constexpr int XR = SSM_STAGE * SSM_COLS / THREADS;                       // x values per thread and chunk
+    constexpr bool PREFETCH = RG > 4;                                        // the variant for prompt portions
     const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int first = cu_seqlens[b], len = cu_seqlens[b + 1] - first;
     if (len <= 0) return;
     const int g = h / (H / G);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int rg = lane >> 3;                                  // which quarter of the rows
-    const int jc = warp * 8 + (lane & 7);                      // column inside the tile
+    const int rg = lane / CPW;                                 // which share of the rows: rows rg * NR .. rg * NR + NR - 1
+    const int jc = warp * CPW + (lane % CPW);                  // column inside the tile
     const int j = tile * SSM_COLS + jc;
     const bool live = j < P;
     float* bc_s = ssm_smem;
-    float* x_s = bc_s + (size_t)SSM_STAGE * 2 * N;
+    float* x_s = bc_s + SSM_STAGE * 2 * NP;
     float* dt_s = x_s + SSM_STAGE * SSM_COLS;
     float* dec_s = dt_s + SSM_STAGE;
     float* S = state + (size_t)slots[b] * slot_stride + ((size_t)h * N) * P;
-    float s[NR];
+    float s[NR];                                               // a padded row stays zero: its B is zero
 #pragma unroll
     for (int i = 0; i < NR; ++i) {
-        const int n = rg + 4 * i;
+        const int n = rg * NR + i;
         s[i] = (live && n < N) ? S[(size_t)n * P + j] : 0.f;
     }
     const float a = expf(A_log[h]), bias = dt_bias[h], d_skip = D[h];
     const int b_col = H * P + g * N, c_col = H * P + G * N + g * N;
+    // Element e of a chunk's [tokens][B | C] belongs to thread e mod THREADS (NR of them per thread), likewise its
+    // [tokens][columns] of x (XR per thread); thread t < tokens has the token's raw step size.
+    auto load_bc = [&](int base, int n_tok, int k) -> float {
+        const int i = threadIdx.x + k * THREADS;
+        const int tt = i / (2 * NP), e = i % (2 * NP), n = e % NP;             // powers of two
+        if (tt >= n_tok || n >= N) return 0.f;
+        return to_f32<T>(xbc[(size_t)(first + base + tt) * xbc_stride + (e < NP ? b_col : c_col) + n]);
+    };
+    auto load_x = [&](int base, int n_tok, int k) -> float {
+        const int i = threadIdx.x + k * THREADS;
+        const int tt = i / SSM_COLS, col = tile * SSM_COLS + i % SSM_COLS;
+        return (tt < n_tok && col < P) ? to_f32<T>(xbc[(size_t)(first + base + tt) * xbc_stride + h * P + col]) : 0.f;
+    };
+    auto load_dt = [&](int base, int n_tok) -> float {
+        return (int)threadIdx.x < n_tok ? to_f32<T>(proj[(size_t)(first + base + threadIdx.x) * proj_stride + dt_col + h]) : 0.f;
+    };
+    // With PREFETCH the next sixteen tokens are on their way into registers while the staged ones run.
+    float pre_bc[PREFETCH ? NR : 1], pre_x[PREFETCH ? XR : 1], pre_dt = 0.f;
+    if (PREFETCH) {
+        const int n0 = min(SSM_STAGE, len);
+#pragma unroll
+        for (int k = 0; k < NR; ++k) pre_bc[PREFETCH ? k : 0] = load_bc(0, n0, k);
+#pragma unroll
+        for (int k = 0; k < XR; ++k) pre_x[PREFETCH ? k : 0] = load_x(0, n0, k);
+        pre_dt = load_dt(0, n0);
+    }
     for (int base = 0; base < len; base += SSM_STAGE) {
         const int n_tok = min(SSM_STAGE, len - base);
         __syncthreads();      // the chunk before has been consumed
-        for (int i = threadIdx.x; i < n_tok * 2 * N; i += blockDim.x) {
-            const int tt = i / (2 * N), k = i - tt * 2 * N;
-            const T* row = xbc + (size_t)(first + base + tt) * xbc_stride;
-            bc_s[i] = to_f32<T>(k < N ? row[b_col + k] : row[c_col + k - N]);
-        }
-        for (int i = threadIdx.x; i < n_tok * SSM_COLS; i += blockDim.x) {
-            const int tt = i / SSM_COLS, c = i - tt * SSM_COLS;
-            const int col = tile * SSM_COLS + c;
-            x_s[i] = col < P ? to_f32<T>(xbc[(size_t)(first + base + tt) * xbc_stride + h * P + col]) : 0.f;
-        }
-        if (threadIdx.x < n_tok) {
-            const float raw = to_f32<T>(proj[(size_t)(first + base + threadIdx.x) * proj_stride + dt_col + h]);
-            const float dt = sm_softplus(__fadd_rn(raw, bias));
+#pragma unroll
+        for (int k = 0; k < NR; ++k)
+            if (PREFETCH || k * THREADS < n_tok * 2 * NP)
+                bc_s[threadIdx.x + k * THREADS] = PREFETCH ? pre_bc[PREFETCH ? k : 0] : load_bc(base, n_tok, k);
+#pragma unroll
+        for (int k = 0; k < XR; ++k)
+            if (PREFETCH || k * THREADS < n_tok * SSM_COLS)
+                x_s[threadIdx.x + k * THREADS] = PREFETCH ? pre_x[PREFETCH ? k : 0] : load_x(base, n_tok, k);
+        if ((int)threadIdx.x < n_tok) {
+            const float dt = sm_softplus(__fadd_rn(PREFETCH ? pre_dt : load_dt(base, n_tok), bias));
             dt_s[threadIdx.x] = dt;
             dec_s[threadIdx.x] = expf(-__fmul_rn(a, dt));
         }
         __syncthreads();
-        for (int tt = 0; tt < n_tok; ++tt) {
-            const float* Bt = bc_s + (size_t)tt * 2 * N;
-            const float* Ct = Bt + N;
-            const float xv = x_s[tt * SSM_COLS + jc];
-            const float dx = __fmul_rn(dt_s[tt], xv), dec = dec_s[tt];
-            float acc = 0.f;
+        if (PREFETCH && base + SSM_STAGE < len) {
+            const int n1 = min(SSM_STAGE, len - base - SSM_STAGE);
 #pragma unroll
-            for (int i = 0; i < NR; ++i) {
-                const int n = rg + 4 * i;
-                if (n < N) {
-                    s[i] = fmaf(dec, s[i], __fmul_rn(dx, Bt[n]));
-                    acc = fmaf(s[i], Ct[n], acc);
+            for (int k = 0; k < NR; ++k) pre_bc[PREFETCH ? k : 0] = load_bc(base + SSM_STAGE, n1, k);
+#pragma unroll
+            for (int k = 0; k < XR; ++k) pre_x[PREFETCH ? k : 0] = load_x(base + SSM_STAGE, n1, k);
+            pre_dt = load_dt(base + SSM_STAGE, n1);
+        }
+        float* yo = y + (size_t)(first + base) * ((size_t)H * P) + (size_t)h * P + j;
+        // one token: the state moves on and the thread's share of y_t comes back
+        auto token = [&](int tt) -> float {
+            const float* Bt = bc_s + tt * 2 * NP + rg * NR;
+            const float* Ct = Bt + NP;
+            const float dx = __fmul_rn(dt_s[tt], x_s[tt * SSM_COLS + jc]), dec = dec_s[tt];
+            float bv[NR], cv[NR];
+            if (NR % 4 == 0) {
+#pragma unroll
+                for (int i = 0; i < NR; i += 4) {
+                    *reinterpret_cast<float4*>(bv + i) = *reinterpret_cast<const float4*>(Bt + i);
+                    *reinterpret_cast<float4*>(cv + i) = *reinterpret_cast<const float4*>(Ct + i);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < NR; i += 2) {
+                    *reinterpret_cast<float2*>(bv + i) = *reinterpret_cast<const float2*>(Bt + i);
+                    *reinterpret_cast<float2*>(cv + i) = *reinterpret_cast<const float2*>(Ct + i);
                 }
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 16);
-            if (live && rg == 0) y[(size_t)(first + base + tt) * ((size_t)H * P) + (size_t)h * P + j] = fmaf(d_skip, xv, acc);
+            float acc0 = 0.f, acc1 = 0.f;                      // two chains: rows of even and of odd i
+#pragma unroll
+            for (int i = 0; i < NR; ++i) {
+                s[i] = fmaf(dec, s[i], __fmul_rn(dx, bv[i]));
+                if (i & 1) acc1 = fmaf(s[i], cv[i], acc1);
+                else acc0 = fmaf(s[i], cv[i], acc0);
+            }
+            return acc0 + acc1;
+        };
+        // a column's shares meet across the lane groups; lane group 0 writes y_t
+        auto finish = [&](int tt, float acc) {
+#pragma unroll
+            for (int o = CPW; o < 32; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (live && rg == 0) yo[(size_t)tt * ((size_t)H * P)] = fmaf(d_skip, x_s[tt * SSM_COLS + jc], acc);
+        };
+        if (PREFETCH && n_tok == SSM_STAGE) {
+            // a whole chunk: the sixteen tokens' shares wait in registers and meet after the loop, so that the shuffles
+            // of one token do not stand in the way of the next token's state (same sums, same order)
+            float part[SSM_STAGE];
+#pragma unroll
+            for (int tt = 0; tt < SSM_STAGE; ++tt) part[tt] = token(tt);
+#pragma unroll
+            for (int tt = 0; tt < SSM_STAGE; ++tt) finish(tt, part[tt]);
+        } else {
+            for (int tt = 0; tt < n_tok; ++tt) finish(tt, token(tt));
         }
     }
     if (live) {
 #pragma unroll
         for (int i = 0; i < NR; ++i) {
-            const int n = rg + 4 * i;
+            const int n = rg * NR + i;
             if (n < N) S[(size_t)n * P + j] = s[i];
         }
     }
 }
 
-template <typename T>
-static int launch_ssm(const void* xbc, long long xbc_stride, const void* proj, long long proj_stride, int dt_col,
-                      const float* dt_bias, const float* A_log, const float* D, float* state, long long slot_stride,
-                      const int* slots, const int* cu_seqlens, float* y, int n_seqs, int H, int G, int P, int N, cudaStream_t stream) {
+template <typename T, int NR, int RG>
+static int launch_ssm_as(const void* xbc, long long xbc_stride, const void* proj, long long proj_stride, int dt_col,
+                         const float* dt_bias, const float* A_log, const float* D, float* state, long long slot_stride,
+                         const int* slots, const int* cu_seqlens, float* y, int n_seqs, int H, int G, int P, int N, cudaStream_t stream) {
     const dim3 grid(ceil_div(P, SSM_COLS), H, n_seqs);
-    const size_t smem = ((size_t)SSM_STAGE * 2 * N + SSM_STAGE * SSM_COLS + 2 * SSM_STAGE) * sizeof(float);
-#define SSM_CASE(NR_)                                                                                                         \
-    do {                                                                                                                      \
-        static bool attr_set[PYRE_MAX_DEVICES] = {};                                                                          \
-        const int dev = pyre_current_device();                                                                                \
-        if (smem > 48 * 1024 && !attr_set[dev]) {                                                                             \
-            cudaFuncSetAttribute(ssm_scan_kernel<T, NR_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);            \
-            attr_set[dev] = true;                                                                                             \
-        }                                                                                                                     \
-        pyre_launch(ssm_scan_kernel<T, NR_>, grid, dim3(128), smem, stream, (const T*)xbc, xbc_stride, (const T*)proj,        \
-                    proj_stride, dt_col, dt_bias, A_log, D, state, slot_stride, slots, cu_seqlens, y, H, G, P, N);            \
-    } while (0)
-    if (N <= 32) SSM_CASE(8);
-    else if (N <= 64) SSM_CASE(16);
-    else if (N <= 128) SSM_CASE(32);
-    else SSM_CASE(64);
-#undef SSM_CASE
+    const size_t smem = ((size_t)SSM_STAGE * 2 * NR * RG + SSM_STAGE * SSM_COLS + 2 * SSM_STAGE) * sizeof(float);
+    pyre_launch(ssm_scan_kernel<T, NR, RG>, grid, dim3(SSM_COLS * RG), smem, stream, (const T*)xbc, xbc_stride, (const T*)proj,
+                proj_stride, dt_col, dt_bias, A_log, D, state, slot_stride, slots, cu_seqlens, y, H, G, P, N);
     PYRE_LAUNCH_CHECK();
     return 0;
 }
 
+template <typename T>
+static int launch_ssm(bool wide, const void* xbc, long long xbc_stride, const void* proj, long long proj_stride, int dt_col,
+                      const float* dt_bias, const float* A_log, const float* D, float* state, long long slot_stride,
+                      const int* slots, const int* cu_seqlens, float* y, int n_seqs, int H, int G, int P, int N, cudaStream_t stream) {
+#define SSM_ARGS xbc, xbc_stride, proj, proj_stride, dt_col, dt_bias, A_log, D, state, slot_stride, slots, cu_seqlens, y, n_seqs, H, G, P, N, stream
+    if (wide) {
+        if (N <= 32) return launch_ssm_as<T, 2, 16>(SSM_ARGS);
+        if (N <= 64) return launch_ssm_as<T, 4, 16>(SSM_ARGS);
+        if (N <= 128) return launch_ssm_as<T, 8, 16>(SSM_ARGS);
+        return launch_ssm_as<T, 16, 16>(SSM_ARGS);
+    }
+    if (N <= 32) return launch_ssm_as<T, 8, 4>(SSM_ARGS);
+    if (N <= 64) return launch_ssm_as<T, 16, 4>(SSM_ARGS);
+    if (N <= 128) return launch_ssm_as<T, 32, 4>(SSM_ARGS);
+    return launch_ssm_as<T, 64, 4>(SSM_ARGS);
+#undef SSM_ARGS
+}
+
+// `wide` != 0: the variant for prompt portions (sixteen warps per tile); 0: the one for steps of single tokens.
 PYRE_API int pyre_ssm_scan(const void* xbc, long long xbc_stride, const void* proj, long long proj_stride, int dt_col,
                            const float* dt_bias, const float* A_log, const float* D, float* state, long long slot_stride,
                            const int* slots, const int* cu_seqlens, float* y, int n_tokens, int n_seqs, int H, int G, int P, int N,
-                           int dtype, cudaStream_t stream) {
+                           int wide, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || P <= 0 || N <= 0 || dt_col < 0 || !state || !slots || !cu_seqlens || !y) return PYRE_ERR_BAD_ARG;
-    if (N > 256) return PYRE_ERR_UNSUPPORTED;
+    if (N > 256) return PYRE_ERR_UNSUPPORTED;      // the staged tokens of a state that large would not fit 48 KB of shared memory either
     if (dtype == PYRE_BF16)
-        return launch_ssm<__nv_bfloat16>(xbc, xbc_stride, proj, proj_stride, dt_col, dt_bias, A_log, D, state, slot_stride, slots,
-                                         cu_seqlens, y, n_seqs, H, G, P, N, stream);
+        return launch_ssm<__nv_bfloat16>(wide != 0, xbc, xbc_stride, proj, proj_stride, dt_col, dt_bias, A_log, D, state, slot_stride,
+                                         slots, cu_seqlens, y, n_seqs, H, G, P, N, stream);
     if (dtype == PYRE_F32)
-        return launch_ssm<float>(xbc, xbc_stride, proj, proj_stride, dt_col, dt_bias, A_log, D, state, slot_stride, slots, cu_seqlens,
-                                 y, n_seqs, H, G, P, N, stream);
+        return launch_ssm<float>(wide != 0, xbc, xbc_stride, proj, proj_stride, dt_col, dt_bias, A_log, D, state, slot_stride, slots,
+                                 cu_seqlens, y, n_seqs, H, G, P, N, stream);
     return PYRE_ERR_BAD_ARG;
 }
 

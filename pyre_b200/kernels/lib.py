@@ -71,7 +71,7 @@ SIGNATURES: dict[str, tuple[str, list]] = {
     "pyre_combine_pairs": ("grouped", [P, P, P, P, P, I, I, I, I, P]),
     "pyre_scale_cap": ("seqmix", [P, LL, F, F, P]),
     "pyre_short_conv": ("seqmix", [P, LL, I, P, P, P, P, LL, LL, P, P, P, P, I, I, I, I, I, I, P]),
-    "pyre_ssm_scan": ("seqmix", [P, LL, P, LL, I, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, I, P]),
+    "pyre_ssm_scan": ("seqmix", [P, LL, P, LL, I, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, I, I, P]),
     "pyre_group_norm_gate": ("seqmix", [P, P, LL, I, I, I, P, F, P, I, I, I, F, I, P]),
     "pyre_diff_combine": ("seqmix", [P, I, F, F, P, I, I, I, I, F, I, P]),
     "pyre_rotate_heads": ("seqmix", [P, LL, I, P, P, I, I, I, I, F, I, P]),

@@ -1927,17 +1927,21 @@ def short_conv(inp: torch.Tensor, col: int, n_ch: int, weight: torch.Tensor, bia
 
 
 SSM_MAX_STATE = 256
+SSM_WIDE_MEAN_LEN = 8      # steps that bring this many tokens per entry or more, on average, take the variant for prompt portions
 
 
 def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
              state_layer: torch.Tensor, slots: torch.Tensor, cu_seqlens: torch.Tensor, n_heads: int, n_groups: int, p_dim: int,
-             n_state: int) -> torch.Tensor:
+             n_state: int, wide: "bool | None" = None) -> torch.Tensor:
     """The selective state-space recurrence over the step's entries, continuing each request's state.  Per head h of
     group h // (n_heads / n_groups), with x_t [p_dim], B_t and C_t [n_state] columns of ``xbc`` ([x: heads * p_dim |
     B: groups * n_state | C: groups * n_state]) and the raw step size column ``dt_col + h`` of ``proj``:
     dt = softplus(raw + dt_bias), S_t = exp(-exp(a_log) dt) S_(t-1) + dt B_t x_t^T, y_t = S_t^T C_t + d_skip x_t.
     ``state_layer`` [slots, floats] fp32 holds S [heads, n_state, p_dim] at the start of slot ``slots[b]``.
-    Token by token in fp32, bit-identical under any cutting.  Returns fp32 [T, heads * p_dim]."""
+    Token by token in fp32.  ``wide``: the kernel variant for prompt portions (a quarter of the rows per thread, four
+    times the warps) instead of the one for single tokens (whole sectors of the state per warp); None: chosen by
+    the mean number of tokens per entry (``SSM_WIDE_MEAN_LEN``).  With one variant results are bit-identical under
+    any cutting; between the two the order of a column's partial sums differs.  Returns fp32 [T, heads * p_dim]."""
     _check(xbc, "xbc", dim=2)
     _check(proj, "proj", xbc.dtype, 2)
     _check(state_layer, "state_layer", torch.float32, 2)
@@ -1956,11 +1960,13 @@ def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.
         raise ValueError("x, B, C or the step sizes do not match the heads and groups")
     if n_heads * n_state * p_dim > state_layer.shape[1] or slots.shape[0] < n_seqs:
         raise ValueError("the state does not lie inside the slot, or slots do not match the batch")
+    if wide is None:
+        wide = T >= SSM_WIDE_MEAN_LEN * max(n_seqs, 1)
     y = torch.empty((T, n_heads * p_dim), dtype=torch.float32, device=xbc.device)
     lib.call("pyre_ssm_scan", xbc.data_ptr(), xbc.shape[1], proj.data_ptr(), proj.shape[1], int(dt_col), dt_bias.data_ptr(),
              a_log.data_ptr(), d_skip.data_ptr(), state_layer.data_ptr(), state_layer.shape[1], slots.data_ptr(),
-             cu_seqlens.data_ptr(), y.data_ptr(), T, n_seqs, int(n_heads), int(n_groups), int(p_dim), int(n_state), _dt(xbc.dtype),
-             _stream())
+             cu_seqlens.data_ptr(), y.data_ptr(), T, n_seqs, int(n_heads), int(n_groups), int(p_dim), int(n_state), int(bool(wide)),
+             _dt(xbc.dtype), _stream())
     return y
 
 

@@ -413,7 +413,7 @@ def short_conv(inp, col, n_ch, weight, bias, state_layer, state_off, slots, seq_
     return out.to(inp.dtype)
 
 
-def ssm_scan(xbc, proj, dt_col, dt_bias, a_log, d_skip, state_layer, slots, cu_seqlens, n_heads, n_groups, p_dim, n_state):
+def ssm_scan(xbc, proj, dt_col, dt_bias, a_log, d_skip, state_layer, slots, cu_seqlens, n_heads, n_groups, p_dim, n_state, wide=None):
     T = xbc.shape[0]
     H, G, P, N = n_heads, n_groups, p_dim, n_state
     v = xbc.float()

@@ -56,7 +56,8 @@ SLOT = {"a": 2, "b": 0, "c": 2}
 # --------------------------------------------------------------------------- the small kernels, each alone
 @pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("C,taps,col,extra,silu,bias,in_bias", [(5, 2, 0, 0, False, False, True), (33, 4, 3, 6, True, True, False),
-                                                               (64, 3, 0, 0, False, False, False), (20, 5, 7, 1, True, True, True)])
+                                                               (64, 3, 0, 0, False, False, False), (20, 5, 7, 1, True, True, True), (130, 8, 2, 0, False, True, False),
+                                                               (7, 9, 0, 3, True, False, True)])
 def test_short_convolution_over_state_slots(ops, dtype, C, taps, col, extra, silu, bias, in_bias):
     """Portions of every size against the convolution of the whole sequence; the history continues from the slot, a
     request that begins finds zeros where an earlier one left its inputs, and the floats beside the history stay."""
@@ -92,9 +93,11 @@ def test_short_convolution_over_state_slots(ops, dtype, C, taps, col, extra, sil
 
 
 @pytest.mark.parametrize("dtype", BOTH)
+@pytest.mark.parametrize("wide", [None, False, True])
 @pytest.mark.parametrize("Hn,G,P,N", [(3, 1, 16, 12), (4, 4, 20, 20), (8, 2, 64, 64), (2, 2, 40, 128), (2, 1, 33, 200), (6, 3, 8, 5)])
-def test_state_space_recurrence_over_state_slots(ops, dtype, Hn, G, P, N):
-    """Step sizes from softplus of large and small arguments, decays from nearly one to nearly zero."""
+def test_state_space_recurrence_over_state_slots(ops, dtype, Hn, G, P, N, wide):
+    """Step sizes from softplus of large and small arguments, decays from nearly one to nearly zero; the kernel's variant
+    for single tokens, the one for prompt portions, and the choice by the step (a state that one left, the other takes up)."""
     cols = Hn * P + 2 * G * N
     xbc = {r: bf16_exact(n, cols, scale=0.7, seed=i) for i, (r, n) in enumerate(SEQ_LENS.items())}
     raw = {r: bf16_exact(n, 3 + Hn, scale=3.0, seed=10 + i) for i, (r, n) in enumerate(SEQ_LENS.items())}
@@ -118,7 +121,7 @@ def test_state_space_recurrence_over_state_slots(ops, dtype, Hn, G, P, N):
         proj = torch.cat([raw[r][at[r]:at[r] + n] for r, n in step]).to(dtype).cuda()
         _, cu = batch([n for _, n in step])
         slots = torch.tensor([SLOT[r] for r, _ in step], dtype=torch.int32, device="cuda")
-        y = ops.ssm_scan(rows, proj, 3, dt_bias.float().cuda(), a_log.float().cuda(), d_skip.float().cuda(), state, slots, cu, Hn, G, P, N)
+        y = ops.ssm_scan(rows, proj, 3, dt_bias.float().cuda(), a_log.float().cuda(), d_skip.float().cuda(), state, slots, cu, Hn, G, P, N, wide=wide)
         assert y.dtype == torch.float32
         k = 0
         for r, n in step:
