@@ -252,7 +252,11 @@ ssm_scan_kernel(const T* xbc, long long xbc_stride, const T* proj, long long pro
     // [tokens][columns] of x (XR per thread); thread t < tokens has the token's raw step size.
     auto load_bc = [&](int base, int n_tok, int k) -> float {
         const int i = threadIdx.x + k * THREADS;
-        const int tt = i / (2 * NP), e = i % (2 * NP), n = e % NP;             // powers of two
+        const int tt = i / (2 * NP), e = i % (2 * NP), at = e % NP;            // powers of two
+        // where row n lies in a token's staged B (and C): lane group r reads its NR rows as vectors of V = min(NR, 4),
+        // and the groups' k-th vectors lie side by side (no two lanes of a load share a bank): [NR / V][RG][V]
+        constexpr int V = NR < 4 ? NR : 4;
+        const int n = ((at / V) % RG) * NR + (at / (V * RG)) * V + at % V;
         if (tt >= n_tok || n >= N) return 0.f;
         return to_f32<T>(xbc[(size_t)(first + base + tt) * xbc_stride + (e < NP ? b_col : c_col) + n]);
     };
@@ -302,21 +306,22 @@ ssm_scan_kernel(const T* xbc, long long xbc_stride, const T* proj, long long pro
         float* yo = y + (size_t)(first + base) * ((size_t)H * P) + (size_t)h * P + j;
         // one token: the state moves on and the thread's share of y_t comes back
         auto token = [&](int tt) -> float {
-            const float* Bt = bc_s + tt * 2 * NP + rg * NR;
+            constexpr int V = NR < 4 ? NR : 4;
+            const float* Bt = bc_s + tt * 2 * NP + rg * V;     // vector k of this lane group at k * RG * V
             const float* Ct = Bt + NP;
             const float dx = __fmul_rn(dt_s[tt], x_s[tt * SSM_COLS + jc]), dec = dec_s[tt];
             float bv[NR], cv[NR];
             if (NR % 4 == 0) {
 #pragma unroll
                 for (int i = 0; i < NR; i += 4) {
-                    *reinterpret_cast<float4*>(bv + i) = *reinterpret_cast<const float4*>(Bt + i);
-                    *reinterpret_cast<float4*>(cv + i) = *reinterpret_cast<const float4*>(Ct + i);
+                    *reinterpret_cast<float4*>(bv + i) = *reinterpret_cast<const float4*>(Bt + i * RG);
+                    *reinterpret_cast<float4*>(cv + i) = *reinterpret_cast<const float4*>(Ct + i * RG);
                 }
             } else {
 #pragma unroll
                 for (int i = 0; i < NR; i += 2) {
-                    *reinterpret_cast<float2*>(bv + i) = *reinterpret_cast<const float2*>(Bt + i);
-                    *reinterpret_cast<float2*>(cv + i) = *reinterpret_cast<const float2*>(Ct + i);
+                    *reinterpret_cast<float2*>(bv + i) = *reinterpret_cast<const float2*>(Bt + i * RG);
+                    *reinterpret_cast<float2*>(cv + i) = *reinterpret_cast<const float2*>(Ct + i * RG);
                 }
             }
             float acc0 = 0.f, acc1 = 0.f;                      // two chains: rows of even and of odd i
