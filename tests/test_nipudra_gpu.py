@@ -374,7 +374,8 @@ def test_routed_feed_forward_of_plain_experts(ops, dtype, T, Hn, ff, E, top, sha
 
 
 # --------------------------------------------------------------------------- the engine against the plain model
-LENGTHS = {"A": [1, 2, 17, 33, 70, 130], "B": [5, 31, 97, 150], "C": [3, 63, 64, 65, 200], "D": [2, 47, 129]}
+LENGTHS = {"A": [1, 2, 17, 33, 70, 130], "B": [5, 31, 97, 120], "C": [3, 63, 64, 65, 130], "D": [2, 47, 129]}
+LONG = {"A": [220, 190], "C": [150, 120]}      # decoded one by one from token 70 (40) on
 
 
 @pytest.fixture(scope="module")
@@ -387,12 +388,14 @@ def models(tmp_path_factory):
         plain = {rid: NH.plain_logits(d, ids) for rid, ids in reqs.items()}
         lowp = {rid: NH.plain_logits(d, ids, lowp=True) for rid, ids in reqs.items()}
         sq = sum(float(((lowp[rid] - plain[rid]) ** 2).sum()) for rid in reqs)
-        out[name] = (d, reqs, plain, math.sqrt(sq / sum(p.size for p in plain.values())), lowp)
+        long_reqs = {f"long{i}": NH.decided_ids(d, L, seed=90 + i) for i, L in enumerate(LONG.get(name, []))}
+        long_plain = {r: (NH.plain_logits(d, ids), NH.plain_logits(d, ids, lowp=True)) for r, ids in long_reqs.items()}
+        out[name] = (d, reqs, plain, math.sqrt(sq / sum(p.size for p in plain.values())), lowp, long_reqs, long_plain)
     return out
 
 
 def run(models, name, dtype, steps, what, rename=None):
-    d, reqs, plain, lowp_rms, lowp = models[name]
+    d, reqs, plain, lowp_rms, lowp = models[name][:5]
     got = H.run_trace_in_process(d, dtype, steps, H.max_live_tokens(steps), NH.NIP_PAGE_SIZE[name])
     if rename:
         plain, lowp = ({new: src[old] for new, old in rename.items()} for src in (plain, lowp))
@@ -466,11 +469,10 @@ def test_mixed_batches_reuse_pages_and_slots(models, name, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_long_decoding(models, name, dtype):
-    """220 tokens, the last 150 or more one by one (captured decode steps), two requests side by side: every window
+    """Up to 220 tokens, the last 80 to 150 one by one (captured decode steps), two requests side by side: every window
     passes over decoded tokens several times and gives pages back on the way, and the recurrent states and the
     convolutions' histories are carried through every step."""
-    d, lowp_rms = models[name][0], models[name][3]
-    reqs = {f"long{i}": NH.decided_ids(d, n, seed=90 + i) for i, n in enumerate([220, 190])}
+    d, lowp_rms, reqs, long_plain = models[name][0], models[name][3], models[name][5], models[name][6]
     steps = [{"step": 0, "entries": [{"id": r, "tokens": ids[:70 - 30 * i], "want": [0]} for i, (r, ids) in enumerate(reqs.items())], "end": []}]
     at = {r: 70 - 30 * i for i, r in enumerate(reqs)}
     while any(at[r] < len(reqs[r]) for r in reqs):
@@ -480,8 +482,8 @@ def test_long_decoding(models, name, dtype):
         steps.append({"step": len(steps), "entries": entries, "end": [e["id"] for e in entries if at[e["id"]] == len(reqs[e["id"]])]})
     got = H.run_trace_in_process(d, dtype, steps, H.max_live_tokens(steps), NH.NIP_PAGE_SIZE[name])
     want, lowp = {}, {}
-    for i, (r, ids) in enumerate(reqs.items()):
-        for dst, full in ((want, NH.plain_logits(d, ids)), (lowp, NH.plain_logits(d, ids, lowp=True))):
+    for i, r in enumerate(reqs):
+        for dst, full in ((want, long_plain[r][0]), (lowp, long_plain[r][1])):
             dst[r] = np.concatenate([full[:1], full[70 - 30 * i:]])
     NH.compare(got, want, dtype, "long decoding", lowp_rms, lowp)
 
