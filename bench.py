@@ -994,10 +994,10 @@ def run_nipudra(args) -> dict:
         moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "top": top}, "shared": {"ff": sh}}
         rot = {"dims": 64, "base": 1e6, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}
         raw_n = {"architecture": "Nipudra", "vocab": V, "width": H, "norm": {"eps": 1e-6}, "embedding": {"scale": H ** 0.5},
-                 "logit_scale": 0.25, "logit_softcap": 30.0, "token_side": {"dim": side}, "layers": [
+                 "logit_scale": 0.5, "logit_softcap": 40.0, "token_side": {"dim": side}, "layers": [
             {"type": "retention", "mixer": {"heads": rh, "dim": rd, "vdim": rd, "decay": [1.0 - 2.0 ** (-5 - 3 * i / rh) for i in range(rh)],
                                             "rot": {"dims": 64, "base": 1e6}}, "mlp": moe},
-            {"type": "attention", "mixer": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "diff": 0.3, "conv": taps,
+            {"type": "attention", "mixer": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "diff": 0.2, "conv": taps,
                                             "mask": {"size": win}, "rot": rot}, "mlp": moe},
             {"type": "mamba2", "mixer": {"heads": mh, "vdim": P, "state": N, "groups": G, "conv": taps, "norm_groups": G}, "mlp": moe}]}
         wh, wd, wr = H // 64, 64, 64

@@ -75,7 +75,7 @@ NIP_B = {"architecture": "Nipudra", "vocab": 333, "width": 92, "norm": {"eps": 3
 # C: sizes of the tensor-core paths: maps of 64 over two key/value heads, retention heads of 64, a state of 64 rows under
 #    heads of 64, a window of 64 on pages of 32, feed-forwards wide enough for the fused products; the reader's window
 #    is smaller than the writer's.
-NIP_C = {"architecture": "Nipudra", "vocab": 640, "width": 256, "norm": {"eps": 1e-6}, "embedding": {"scale": 16.0},
+NIP_C = {"architecture": "Nipudra", "vocab": 512, "width": 256, "norm": {"eps": 1e-6}, "embedding": {"scale": 16.0},
          "logit_scale": 0.125, "logit_softcap": 50.0, "token_side": {"dim": 16}, "layers": [
     with_mlp(mamba(8, 64, 64, 2, 4, 2), moe(128, 8, 2, 256)),
     with_mlp(attn(4, 2, 64, 64, 0.12, 0.2, 4, 64, 64, 500000.0, (3.0, 256, 16.0, 2.0)), moe(128, 8, 2, 256)),

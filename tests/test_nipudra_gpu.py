@@ -190,12 +190,12 @@ def test_side_slice_gate_shared_gate_and_cap(ops, dtype):
     got = ops.token_gate_add(acc.float().cuda(), h.to(dtype).cuda(), w.float().cuda(), y.to(dtype).cuda())
     close(got, acc + torch.sigmoid(h @ w)[:, None] * y, torch.float32, "one gate per token", atol32=1e-5)
     x = bf16_exact(T, Wn, scale=30.0, seed=7)
-    close(ops.scale_cap(x.float().cuda(), 0.25, 20.0), 20.0 * torch.tanh(x * 0.25 / 20.0), torch.float32, "cap", atol32=1e-5)
+    close(ops.scale_cap(x.float().cuda(), 0.5, 20.0), 20.0 * torch.tanh(x * 0.5 / 20.0), torch.float32, "cap", atol32=1e-5)
     close(ops.scale_cap(x.float().cuda(), 3.0), x * 3.0, torch.float32, "factor")
 
 
 @pytest.mark.parametrize("dtype", BOTH)
-@pytest.mark.parametrize("E,top", [(5, 2), (3, 3), (1, 1), (12, 4), (40, 1)])
+@pytest.mark.parametrize("E,top", [(5, 2), (3, 3), (1, 1), (10, 4), (40, 1)])
 def test_router_with_bias_and_weights_over_the_chosen(ops, dtype, E, top):
     T, Hn = 11, 92
     h, w, b = bf16_exact(T, Hn, seed=E), bf16_exact(E, Hn, scale=0.3, seed=E + 1), bf16_exact(E, scale=2.0, seed=E + 2)
@@ -305,11 +305,12 @@ def check_mixer(tmp_path, layer, width, eps, dtype, page, plain, seed, wrong=Non
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,kv,dk,dv,conv,window,rot,page,width", [
     (4, 2, 16, 24, 3, 11, 8, 16, 96), (5, 5, 20, 12, 0, 0, 0, 8, 92), (4, 2, 64, 64, 4, 64, 64, 32, 256), (6, 1, 48, 40, 4, 100000, 16, 16, 128),
-    (2, 2, 32, 32, 2, 1, 0, 16, 64), (6, 3, 12, 20, 5, 7, 12, 8, 92), (2, 1, 16, 16, 4, 16, 16, 16, 64), (3, 1, 32, 16, 2, 17, 32, 16, 72)])
+    (2, 2, 32, 32, 2, 1, 0, 16, 64), (6, 3, 12, 20, 5, 7, 12, 8, 92), (2, 1, 16, 16, 4, 16, 16, 16, 64), (3, 1, 32, 16, 2, 17, 32, 16, 72),
+    (2, 1, 64, 128, 3, 40, 32, 16, 128), (4, 4, 128, 96, 4, 33, 64, 32, 256)])
 def test_differential_attention_alone(tmp_path, dtype, heads, kv, dk, dv, conv, window, rot, page, width):
     """Windows of 1 (a token sees itself only), of a page, one more than a page, smaller and larger than a page, and none
     at all; the keys just inside and just outside: the plain result with a window one shorter or longer is far off."""
-    layer = NH.attn(heads, kv, dk, dv, 0.8 / math.sqrt(dk), 0.3, conv, window, rot, 100.0, (8.0, 32, 4.0, 1.0) if rot else None)
+    layer = NH.attn(heads, kv, dk, dv, 0.8 / math.sqrt(dk), 0.35, conv, window, rot, 100.0, (8.0, 32, 4.0, 1.0) if rot else None)
     mixer = layer["mixer"]
 
     def plain(h, w, m=mixer):
@@ -488,18 +489,19 @@ def test_long_decoding(models, name, dtype):
     NH.compare(got, want, dtype, "long decoding", lowp_rms, lowp)
 
 
-@pytest.mark.parametrize("name", ["A", "C"])
-def test_greedy_generation_through_the_engine(models, name):
+@pytest.mark.parametrize("name,seqs,pages", [("A", 3, 5), ("C", 3, 5), ("A", 6, 14)])
+def test_greedy_generation_through_the_engine(models, name, seqs, pages):
     """``Engine.generate`` (scheduler, portions of prompts, captured decode steps, sampler) gives the tokens that
     the plain implementation's argmax gives, in 32-bit; a cache too small for all requests at once makes the
-    scheduler preempt and recompute, state slots included."""
+    scheduler preempt and recompute, state slots included; six requests side by side decode in captured steps that are
+    padded with rows of no request (the scratch page and the scratch state slot)."""
     from pyre_b200.engine.engine import Engine
     from pyre_b200.sampling import SamplingParams
     d = models[name][0]
     raw = NH.NIP[name]
-    prompts = [H.random_ids(raw["vocab"], n, seed=40 + n) for n in (15, 16, 3, 30)]
+    prompts = [H.random_ids(raw["vocab"], n, seed=40 + n) for n in ((15, 16, 3, 30) if seqs == 3 else (15, 16, 3, 30, 7, 11))]
     new = 12
-    engine = Engine(str(d), dtype="float32", page_size=16, num_pages=5, max_num_seqs=3, max_num_batched_tokens=32, prefill_chunk=20)
+    engine = Engine(str(d), dtype="float32", page_size=16, num_pages=pages, max_num_seqs=seqs, max_num_batched_tokens=32, prefill_chunk=20)
     outs = engine.generate(prompts, SamplingParams(max_new_tokens=new, return_logits=True))
     for p, o in zip(prompts, outs):
         ids = list(p)
