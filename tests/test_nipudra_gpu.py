@@ -56,7 +56,7 @@ SLOT = {"a": 2, "b": 0, "c": 2}
 # --------------------------------------------------------------------------- the small kernels, each alone
 @pytest.mark.parametrize("dtype", BOTH)
 @pytest.mark.parametrize("C,taps,col,extra,silu,bias,in_bias", [(5, 2, 0, 0, False, False, True), (33, 4, 3, 6, True, True, False),
-                                                               (64, 3, 0, 0, False, False, False), (20, 5, 7, 1, True, True, True), (130, 8, 2, 0, False, True, False),
+                                                               (64, 3, 0, 0, False, False, False), (20, 5, 7, 1, True, True, True), (130, 8, 2, 0, False, True, False), (48, 4, 8, 8, True, True, True), (256, 2, 16, 0, False, False, False),
                                                                (7, 9, 0, 3, True, False, True)])
 def test_short_convolution_over_state_slots(ops, dtype, C, taps, col, extra, silu, bias, in_bias):
     """Portions of every size against the convolution of the whole sequence; the history continues from the slot, a
